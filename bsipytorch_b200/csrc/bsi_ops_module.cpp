@@ -1,0 +1,603 @@
+// pybind11 module `bsi_ops`: the reference's CUDA entry points (bsi_ops/csrc/cuda/bsi_cuda.cpp:
+// 1010-1078) with the same names, argument order, defaults, return tuples and capsule names, on
+// top of the bsi_b200 C ABI. Host logic only: tensors are allocated here, every kernel lives in
+// libbsi_b200.so.
+//
+// Mode: the fixed-bit block-floating path of the reference (queries BSI_FIXED_BITS_QUERIES bits,
+// default 7, with per-256-element chunk scales when BSI_FIXED_CHUNK_SCALE != 0, default on; keys
+// BSI_FIXED_BITS_KEYS bits, default 6, per-row scale). The reference needs those variables to be
+// set to reach this path (its README's fixed76 recipe); here they are the defaults. The
+// variable-slice mode (bits = 0), which needs the un-vendored bsiCPP key builder, is rejected.
+#include <torch/extension.h>
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <cuda_runtime_api.h>
+
+#include <cmath>
+#include <cstdlib>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "bsi_b200.h"
+
+namespace py = pybind11;
+
+namespace {
+
+// ---- environment (bsi_vector_cuda.cpp:254-358, bsi_cuda.cpp:108-143) ----------------------------
+int env_int(const char* name, int fallback) {
+    const char* s = std::getenv(name);
+    return s ? std::atoi(s) : fallback;
+}
+
+int fixed_bits(const char* specific, int fallback) {
+    int v = fallback;
+    if (const char* s = std::getenv(specific)) v = std::atoi(s);
+    else if (const char* g = std::getenv("BSI_FIXED_BITS")) v = std::atoi(g);
+    TORCH_CHECK(v > 0, specific, "=0 selects the reference's variable-slice mode, which this build does not provide "
+                "(it depends on the bsiCPP key builder); use fixed bits in [2, 8]");
+    TORCH_CHECK(v >= 2 && v <= 8, specific, " must be in [2, 8] for the int8 tensor-core path, got ", v);
+    return v;
+}
+int bits_queries() { return fixed_bits("BSI_FIXED_BITS_QUERIES", 7); }
+int bits_keys() { return fixed_bits("BSI_FIXED_BITS_KEYS", 6); }
+bool chunk_scale_enabled() { return env_int("BSI_FIXED_CHUNK_SCALE", 1) != 0; }
+bool profile_enabled() { return env_int("BSI_PROFILE", 0) != 0; }
+void check_clip() {
+    const char* s = std::getenv("BSI_FIXED_CLIP_K");
+    TORCH_CHECK(!(s && std::strtof(s, nullptr) > 0.0f), "BSI_FIXED_CLIP_K > 0 (outlier clipping) is not supported");
+}
+int engine_from_env() {
+    const char* s = std::getenv("BSI_B200_ENGINE");
+    if (!s || !*s || std::string(s) == "auto") return BSI_ENGINE_AUTO;
+    const std::string v(s);
+    if (v == "tcgen05") return BSI_ENGINE_TCGEN05;
+    if (v == "simt") return BSI_ENGINE_SIMT;
+    if (v == "bmma") return BSI_ENGINE_BMMA;
+    if (v.rfind("tcgen05:", 0) == 0) return 1000 + std::atoi(v.c_str() + 8);  // pinned tile width
+    TORCH_CHECK(false, "BSI_B200_ENGINE must be auto, tcgen05, tcgen05:<64|128|256>, simt or bmma");
+}
+
+void check_status(int rc, const char* what) {
+    TORCH_CHECK(rc == BSI_OK, what, " failed: ", bsi_b200_status_string(rc), " (", bsi_b200_last_error(), ")");
+}
+
+bsi_stream_t current_stream() { return static_cast<bsi_stream_t>(at::cuda::getCurrentCUDAStream().stream()); }
+
+int dtype_code(const at::Tensor& t) {
+    if (t.scalar_type() == at::kHalf) return BSI_DTYPE_F16;
+    if (t.scalar_type() == at::kBFloat16) return BSI_DTYPE_BF16;
+    return BSI_DTYPE_F32;
+}
+
+at::Tensor slice_weight_base(int S, const at::Device& dev) {
+    // +-2^i with the top slice negative (bsi_cuda.cpp:217-236, bsi_vector_cuda.cpp:1028).
+    std::vector<float> w(S);
+    for (int i = 0; i < S; ++i) w[i] = std::ldexp(1.0f, i) * ((i == S - 1) ? -1.0f : 1.0f);
+    return torch::tensor(w, torch::dtype(torch::kFloat32)).to(dev);
+}
+
+// ---- holders behind the capsules (bsi_cuda.cpp:146-215) ------------------------------------------
+struct PackedBatch {
+    at::Tensor words;          // [rows, S, W] int64
+    at::Tensor slice_weights;  // [rows, S] float32
+    at::Tensor scales;         // [rows, chunks] (chunk mode) or [rows] (row mode) float32: 2^shift
+    at::Tensor q8;             // [rows, ld8] int8
+    bool chunk_mode = false;
+    int S = 0;
+    int W = 0;
+    int64_t rows = 0;
+    int64_t d = 0;
+    int64_t chunks = 0;
+    int decimals = 0;
+    float quantize_ms = 0.f;
+};
+
+struct PrebuiltBSIKeysCUDA {
+    PackedBatch b;
+    int64_t num_keys = 0;
+    float threshold = 0.2f;
+};
+
+struct PrebuiltBSIQueryBatchCUDA {
+    PackedBatch b;
+    size_t mem_bytes = 0;
+};
+
+struct PrebuiltBSIQueryCUDA {
+    std::shared_ptr<PackedBatch> parent;  // the batch this row is a view of
+    int64_t row = 0;
+    bool twos_complement = false;
+    size_t mem_bytes = 0;
+};
+
+template <typename T>
+T* from_capsule(const py::capsule& cap, const char* name) {
+    TORCH_CHECK(cap.name() != nullptr && std::string(cap.name()) == name, "Expected a ", name, " capsule");
+    return reinterpret_cast<T*>(cap.get_pointer());
+}
+
+uint64_t g_last_quantize_ns = 0, g_last_pack_ns = 0, g_last_total_ns = 0;
+
+// Quantise + pack `x` ([rows, d], f32/f16/bf16, CPU or CUDA) in one kernel.
+PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chunk_mode, bool profile) {
+    TORCH_CHECK(input.dim() == 2, "expects 2D tensor [rows, d]");
+    check_clip();
+    const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
+    at::Tensor x = input.detach();
+    if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
+        x = x.to(at::kFloat);
+    x = x.to(dev, /*non_blocking=*/false).contiguous();
+
+    PackedBatch b;
+    b.rows = x.size(0);
+    b.d = x.size(1);
+    b.S = bits;
+    b.W = b.d > 0 ? static_cast<int>((b.d + 63) / 64) : 1;
+    b.chunks = (b.d + 255) / 256;
+    b.decimals = decimal_places;
+    b.chunk_mode = chunk_mode;
+    const int64_t ld8 = std::max<int64_t>(b.chunks, 1) * 256;
+    auto opt = [&](at::ScalarType t) { return at::TensorOptions().dtype(t).device(dev); };
+    // Partial last words / empty inputs rely on zero-initialised words, as the reference's do.
+    const bool ragged = (b.d % 64) != 0 || b.rows == 0 || b.d == 0;
+    b.words = ragged ? at::zeros({b.rows, bits, b.W}, opt(at::kLong)) : at::empty({b.rows, bits, b.W}, opt(at::kLong));
+    if (chunk_mode) b.scales = at::ones({b.rows, std::max<int64_t>(b.chunks, 0)}, opt(at::kFloat));
+    else b.scales = at::ones({b.rows}, opt(at::kFloat));
+    b.q8 = at::empty({b.rows, ld8}, opt(at::kChar));
+    if (b.rows == 0 || b.d == 0) {
+        b.q8.zero_();
+        b.slice_weights = slice_weight_base(bits, dev).unsqueeze(0).expand({b.rows, bits}).contiguous();
+        return b;
+    }
+
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    auto stream = at::cuda::getCurrentCUDAStream();
+    if (profile) {
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, stream.stream());
+    }
+    check_status(bsi_b200_quantize_pack(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, bits,
+                                        chunk_mode ? 1 : 0,
+                                        reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
+                                        b.scales.data_ptr<float>(), nullptr, b.q8.data_ptr<int8_t>(), ld8,
+                                        current_stream()),
+                 "bsi_b200_quantize_pack");
+    if (profile) {
+        cudaEventRecord(e1, stream.stream());
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(&b.quantize_ms, e0, e1);
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+    auto base = slice_weight_base(bits, dev).unsqueeze(0);
+    if (chunk_mode) b.slice_weights = base.expand({b.rows, bits}).contiguous();
+    else b.slice_weights = (base * b.scales.unsqueeze(1)).contiguous();  // bsi_vector_cuda.cpp:1042,1157
+    return b;
+}
+
+// Queries get chunk scales when enabled and the word count allows 256-bit chunks
+// (bsi_vector_cuda.cpp:980-994).
+PackedBatch pack_queries(const at::Tensor& q2d, int decimal_places) {
+    const int bits = bits_queries();
+    const int64_t d = q2d.size(1);
+    const int W = d > 0 ? static_cast<int>((d + 63) / 64) : 1;
+    const bool chunk = chunk_scale_enabled() && (W % 4 == 0);
+    const bool profile = profile_enabled() && q2d.is_cuda();
+    PackedBatch b = pack(q2d, decimal_places, bits, chunk, profile);
+    // One fused kernel does quantise and pack; its time is reported as the pack time.
+    g_last_quantize_ns = 0;
+    g_last_pack_ns = profile ? static_cast<uint64_t>(b.quantize_ms * 1.0e6) : 0;
+    g_last_total_ns = g_last_pack_ns;
+    return b;
+}
+
+size_t batch_mem_bytes(const PackedBatch& b) {
+    size_t n = static_cast<size_t>(b.words.numel() * b.words.element_size()) +
+               static_cast<size_t>(b.slice_weights.numel() * b.slice_weights.element_size());
+    if (b.chunk_mode) n += static_cast<size_t>(b.scales.numel() * b.scales.element_size());
+    return n;
+}
+
+// ---- builders -------------------------------------------------------------------------------------
+py::tuple build_bsi_keys_cuda(torch::Tensor K, int decimalPlaces, float compress_threshold) {
+    TORCH_CHECK(K.dim() == 2, "K must be 2D [num_keys, d]");
+    auto* holder = new PrebuiltBSIKeysCUDA();
+    holder->b = pack(K, decimalPlaces, bits_keys(), /*chunk_mode=*/false, /*profile=*/false);
+    holder->num_keys = K.size(0);
+    holder->threshold = compress_threshold;
+    const uint64_t total_mem_bytes = static_cast<uint64_t>(holder->b.words.numel() * holder->b.words.element_size());
+    py::capsule cap(holder, "PrebuiltBSIKeysCUDA", [](PyObject* c) {
+        delete reinterpret_cast<PrebuiltBSIKeysCUDA*>(PyCapsule_GetPointer(c, "PrebuiltBSIKeysCUDA"));
+    });
+    return py::make_tuple(cap, total_mem_bytes, holder->num_keys, K.size(1), holder->b.W);
+}
+
+py::capsule build_bsi_queries_cuda_batch_packed(torch::Tensor q2d, int decimalPlaces, float compress_threshold) {
+    TORCH_CHECK(q2d.dim() == 2, "q must be 2D [Q, d]");
+    (void)compress_threshold;  // ignored by the reference too (bsi_cuda.cpp:350)
+    auto* holder = new PrebuiltBSIQueryBatchCUDA();
+    holder->b = pack_queries(q2d, decimalPlaces);
+    holder->mem_bytes = batch_mem_bytes(holder->b);
+    return py::capsule(holder, "PrebuiltBSIQueryBatchCUDA", [](PyObject* c) {
+        delete reinterpret_cast<PrebuiltBSIQueryBatchCUDA*>(PyCapsule_GetPointer(c, "PrebuiltBSIQueryBatchCUDA"));
+    });
+}
+
+py::capsule row_capsule(const std::shared_ptr<PackedBatch>& parent, int64_t row, bool twos) {
+    auto* h = new PrebuiltBSIQueryCUDA();
+    h->parent = parent;
+    h->row = row;
+    h->twos_complement = twos;
+    h->mem_bytes = static_cast<size_t>(parent->S) * static_cast<size_t>(parent->W) * sizeof(int64_t);
+    return py::capsule(h, "PrebuiltBSIQueryCUDA", [](PyObject* c) {
+        delete reinterpret_cast<PrebuiltBSIQueryCUDA*>(PyCapsule_GetPointer(c, "PrebuiltBSIQueryCUDA"));
+    });
+}
+
+py::list build_bsi_queries_cuda_batch(torch::Tensor q2d, int decimalPlaces, float compress_threshold) {
+    TORCH_CHECK(q2d.dim() == 2, "q must be 2D [Q, d]");
+    (void)compress_threshold;
+    auto parent = std::make_shared<PackedBatch>(pack_queries(q2d, decimalPlaces));
+    py::list out;
+    for (int64_t qi = 0; qi < parent->rows; ++qi) out.append(row_capsule(parent, qi, false));
+    return out;
+}
+
+// 1-D query: one scale for the whole vector folded into the slice weights
+// (bsi_vector_cuda.cpp:778-852, bsi_cuda.cpp:238-270).
+py::tuple build_bsi_query_cuda(torch::Tensor q, int decimalPlaces, float compress_threshold) {
+    TORCH_CHECK(q.dim() == 1, "q must be 1D [d]");
+    (void)compress_threshold;
+    auto parent = std::make_shared<PackedBatch>(
+        pack(q.unsqueeze(0), decimalPlaces, bits_queries(), /*chunk_mode=*/false, /*profile=*/false));
+    const bool has_negative = q.numel() > 0 && parent->q8.lt(0).any().item<bool>();
+    py::capsule cap = row_capsule(parent, 0, has_negative);
+    const uint64_t mem = static_cast<uint64_t>(parent->words.numel() * parent->words.element_size());
+    return py::make_tuple(cap, mem, parent->S, parent->W);
+}
+
+// ---- EWAH helpers ---------------------------------------------------------------------------------
+struct EwahStream {
+    at::Tensor stream, off, len, flags;
+    int64_t total = 0;
+};
+
+EwahStream ewah_encode(const at::Tensor& words2d, double threshold) {
+    TORCH_CHECK(words2d.dim() == 2 && words2d.scalar_type() == at::kLong && words2d.is_cuda(),
+                "words must be a CUDA int64 tensor [S, W]");
+    auto w = words2d.contiguous();
+    const int64_t S = w.size(0), W = w.size(1);
+    auto o64 = at::TensorOptions().dtype(at::kLong).device(w.device());
+    auto o32 = at::TensorOptions().dtype(at::kInt).device(w.device());
+    EwahStream e;
+    e.off = at::empty({S}, o64);
+    e.len = at::empty({S}, o32);
+    e.flags = at::empty({S}, o32);
+    auto total = at::zeros({1}, o64);
+    const int64_t capacity = S * (W + 1);  // worst case: every slice verbatim, or alternating words
+    e.stream = at::empty({std::max<int64_t>(capacity, 1)}, o64);
+    auto scratch = at::empty({std::max<int64_t>(bsi_b200_ewah_scratch_bytes(S), 8)},
+                             at::TensorOptions().dtype(at::kByte).device(w.device()));
+    if (S > 0) {
+        check_status(bsi_b200_ewah_encode(reinterpret_cast<const uint64_t*>(w.data_ptr<int64_t>()), S, W, threshold,
+                                          scratch.data_ptr(), scratch.numel(),
+                                          reinterpret_cast<uint64_t*>(e.stream.data_ptr<int64_t>()), capacity,
+                                          reinterpret_cast<uint64_t*>(e.off.data_ptr<int64_t>()),
+                                          e.len.data_ptr<int>(), e.flags.data_ptr<int>(),
+                                          reinterpret_cast<uint64_t*>(total.data_ptr<int64_t>()), current_stream()),
+                     "bsi_b200_ewah_encode");
+    }
+    e.total = total.item<int64_t>();
+    e.stream = e.stream.narrow(0, 0, e.total);
+    return e;
+}
+
+at::Tensor ewah_decode(const EwahStream& e, int64_t W) {
+    const int64_t S = e.off.size(0);
+    auto out = at::empty({S, W}, at::TensorOptions().dtype(at::kLong).device(e.off.device()));
+    if (S > 0) {
+        check_status(bsi_b200_ewah_decode(reinterpret_cast<const uint64_t*>(e.stream.data_ptr<int64_t>()),
+                                          reinterpret_cast<const uint64_t*>(e.off.data_ptr<int64_t>()),
+                                          e.len.data_ptr<int>(), S, W,
+                                          reinterpret_cast<uint64_t*>(out.data_ptr<int64_t>()), current_stream()),
+                     "bsi_b200_ewah_decode");
+    }
+    return out;
+}
+
+// EWAH round trip of a 1-D query (bsi_cuda.cpp:386-431): encode the slices, decode them back into
+// the verbatim words the dot consumes; mem_bytes = compressed + verbatim.
+py::tuple build_bsi_query_cuda_hybrid(torch::Tensor q, int decimalPlaces, double compress_threshold) {
+    TORCH_CHECK(q.dim() == 1, "q must be 1D [d]");
+    auto parent = std::make_shared<PackedBatch>(
+        pack(q.unsqueeze(0), decimalPlaces, bits_queries(), /*chunk_mode=*/false, /*profile=*/false));
+    const bool has_negative = q.numel() > 0 && parent->q8.lt(0).any().item<bool>();
+    auto words2d = parent->words.view({parent->S, parent->W});
+    EwahStream e = ewah_encode(words2d, compress_threshold);
+    parent->words = ewah_decode(e, parent->W).view({1, parent->S, parent->W});
+    py::capsule cap = row_capsule(parent, 0, has_negative);
+    const uint64_t mem = static_cast<uint64_t>(e.total * 8 + parent->words.numel() * parent->words.element_size());
+    reinterpret_cast<PrebuiltBSIQueryCUDA*>(cap.get_pointer())->mem_bytes = mem;
+    return py::make_tuple(cap, mem, parent->S, parent->W);
+}
+
+// ---- dot ------------------------------------------------------------------------------------------
+py::tuple run_dot(const PackedBatch& qb, const PrebuiltBSIKeysCUDA& keys, bool want_iacc, at::Tensor* iacc_out) {
+    const int64_t Q = qb.rows, R = keys.num_keys;
+    TORCH_CHECK(Q > 0 && qb.S > 0 && qb.W > 0, "Empty query batch");
+    TORCH_CHECK(qb.W == keys.b.W, "Word count mismatch between query batch and keys");
+    TORCH_CHECK(R > 0, "Empty keys");
+    TORCH_CHECK(qb.decimals == keys.b.decimals, "Decimal mismatch between queries and keys: q=", qb.decimals,
+                " k=", keys.b.decimals);
+    if (qb.chunk_mode) TORCH_CHECK(keys.b.W % 4 == 0, "Chunk scales require W64 multiple of 4");
+    const int total_decimals = qb.decimals + keys.b.decimals;
+    const double scale_inv = total_decimals > 0 ? 1.0 / std::pow(10.0, total_decimals) : 1.0;  // bsi_cuda.cpp:710-711
+
+    auto fopt = at::TensorOptions().dtype(at::kFloat).device(qb.q8.device());
+    at::Tensor out = at::empty({Q, R}, fopt);
+    at::Tensor iacc;
+    if (want_iacc) iacc = at::empty({Q, R, qb.chunks}, fopt.dtype(at::kInt));
+
+    const bool profile = profile_enabled();
+    auto stream = at::cuda::getCurrentCUDAStream();
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    float kernel_ms = 0.f;
+    if (profile) {
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        cudaEventRecord(e0, stream.stream());
+    }
+    const int engine = engine_from_env();
+    const int64_t qs_stride = qb.chunk_mode ? qb.chunks : 0;
+    if (engine == BSI_ENGINE_BMMA) {
+        check_status(bsi_b200_dot_words(reinterpret_cast<const uint64_t*>(qb.words.data_ptr<int64_t>()),
+                                        qb.scales.data_ptr<float>(), qs_stride, qb.S, qb.W,
+                                        reinterpret_cast<const uint64_t*>(keys.b.words.data_ptr<int64_t>()),
+                                        keys.b.slice_weights.data_ptr<float>(), keys.b.S, R, Q,
+                                        static_cast<float>(scale_inv), R, out.data_ptr<float>(),
+                                        want_iacc ? iacc.data_ptr<int>() : nullptr, current_stream()),
+                     "bsi_b200_dot_words");
+    } else {
+        check_status(bsi_b200_dot_i8(qb.q8.data_ptr<int8_t>(), qb.q8.size(1), qb.scales.data_ptr<float>(), qs_stride,
+                                     keys.b.q8.data_ptr<int8_t>(), keys.b.q8.size(1), keys.b.scales.data_ptr<float>(),
+                                     Q, R, qb.chunks, static_cast<float>(scale_inv), out.data_ptr<float>(), R,
+                                     want_iacc ? iacc.data_ptr<int>() : nullptr, engine, current_stream()),
+                     "bsi_b200_dot_i8");
+    }
+    if (profile) {
+        cudaEventRecord(e1, stream.stream());
+        cudaEventSynchronize(e1);
+        cudaEventElapsedTime(&kernel_ms, e0, e1);
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    }
+    if (iacc_out) *iacc_out = iacc;
+    const uint64_t ns_total = static_cast<uint64_t>(kernel_ms * 1.0e6);
+    const double per_query = Q > 0 ? static_cast<double>(ns_total) / static_cast<double>(Q) : 0.0;
+    const double per_scalar = (Q > 0 && R > 0) ? static_cast<double>(ns_total) / (static_cast<double>(Q) * R) : 0.0;
+    return py::make_tuple(out, ns_total, per_query, per_scalar);
+}
+
+py::tuple batch_dot_product_multiquery_cuda_batch_caps(py::capsule query_batch_cap, py::capsule keyset_cuda_cap) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(keys != nullptr, "Invalid CUDA keys capsule");
+    auto* qb = from_capsule<PrebuiltBSIQueryBatchCUDA>(query_batch_cap, "PrebuiltBSIQueryBatchCUDA");
+    TORCH_CHECK(qb != nullptr, "Invalid CUDA query-batch capsule");
+    return run_dot(qb->b, *keys, false, nullptr);
+}
+
+// Rebuilds a batch from per-row capsules. Rows that are, in order, all the rows of one parent
+// batch (what build_bsi_queries_cuda_batch returns) reuse it without copying; any other list is
+// gathered row by row (the reference always re-stacks, bsi_cuda.cpp:487-518).
+PackedBatch batch_from_list(const py::list& caps) {
+    const int64_t Q = static_cast<int64_t>(py::len(caps));
+    std::vector<PrebuiltBSIQueryCUDA*> rows(Q);
+    for (int64_t i = 0; i < Q; ++i) {
+        TORCH_CHECK(py::isinstance<py::capsule>(caps[i]), "Each item must be a capsule");
+        rows[i] = from_capsule<PrebuiltBSIQueryCUDA>(py::cast<py::capsule>(caps[i]), "PrebuiltBSIQueryCUDA");
+        TORCH_CHECK(rows[i] != nullptr && rows[i]->parent, "Invalid BSI query capsule at index ", i);
+    }
+    const auto& p0 = rows[0]->parent;
+    bool whole = (p0->rows == Q);
+    for (int64_t i = 0; i < Q && whole; ++i) whole = (rows[i]->parent == p0 && rows[i]->row == i);
+    if (whole) return *p0;
+    PackedBatch b;
+    b.S = p0->S; b.W = p0->W; b.d = p0->d; b.chunks = p0->chunks; b.decimals = p0->decimals;
+    b.chunk_mode = p0->chunk_mode; b.rows = Q;
+    std::vector<at::Tensor> words, weights, scales, q8;
+    for (int64_t i = 0; i < Q; ++i) {
+        const auto& p = rows[i]->parent;
+        TORCH_CHECK(p->W == b.W, "Word count mismatch across queries");
+        TORCH_CHECK(p->decimals == b.decimals, "Decimal mismatch across queries not supported");
+        TORCH_CHECK(p->S == b.S, "Mixed slice counts across queries are not supported in fixed-bit mode");
+        TORCH_CHECK(p->chunk_mode == b.chunk_mode, "Mixed chunk-scale and non-chunk-scale queries in the same group");
+        words.push_back(p->words[rows[i]->row]);
+        weights.push_back(p->slice_weights[rows[i]->row]);
+        scales.push_back(p->scales[rows[i]->row]);
+        q8.push_back(p->q8[rows[i]->row]);
+    }
+    b.words = at::stack(words).contiguous();
+    b.slice_weights = at::stack(weights).contiguous();
+    b.scales = at::stack(scales).contiguous();
+    b.q8 = at::stack(q8).contiguous();
+    return b;
+}
+
+py::tuple batch_dot_product_multiquery_cuda_caps(py::list query_caps_list, py::capsule keyset_cuda_cap) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(keys != nullptr, "Invalid CUDA keys capsule");
+    TORCH_CHECK(keys->num_keys > 0 && py::len(query_caps_list) > 0, "Empty keys or queries");
+    PackedBatch b = batch_from_list(query_caps_list);
+    return run_dot(b, *keys, false, nullptr);
+}
+
+// ---- stats ----------------------------------------------------------------------------------------
+py::dict bsi_keys_cuda_stats(py::capsule keyset_cuda_cap) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    py::dict sb;
+    sb[py::int_(keys->b.S)] = py::int_(keys->num_keys);
+    py::dict out;
+    out["W"] = py::int_(keys->b.W);
+    out["d"] = py::int_(keys->b.d);
+    out["num_keys"] = py::int_(keys->num_keys);
+    out["decimals"] = py::int_(keys->b.decimals);
+    out["threshold"] = py::float_(keys->threshold);
+    out["Sb_counts"] = sb;
+    return out;
+}
+
+py::dict bsi_query_caps_stats(py::list query_caps_list) {
+    const int64_t Q = static_cast<int64_t>(py::len(query_caps_list));
+    TORCH_CHECK(Q > 0, "Empty query capsule list");
+    std::unordered_map<int, int64_t> counts;
+    int W = -1;
+    for (int64_t i = 0; i < Q; ++i) {
+        TORCH_CHECK(py::isinstance<py::capsule>(query_caps_list[i]), "Each item must be a capsule");
+        auto* q = from_capsule<PrebuiltBSIQueryCUDA>(py::cast<py::capsule>(query_caps_list[i]), "PrebuiltBSIQueryCUDA");
+        counts[q->parent->S] += 1;
+        if (W < 0) W = q->parent->W;
+        else TORCH_CHECK(q->parent->W == W, "Word count mismatch across queries");
+    }
+    py::dict s_counts;
+    for (const auto& kv : counts) s_counts[py::int_(kv.first)] = py::int_(kv.second);
+    py::dict out;
+    out["Q"] = py::int_(Q);
+    out["W"] = py::int_(W);
+    out["S_counts"] = s_counts;
+    return out;
+}
+
+std::string cuda_builder_version() { return "BSI_B200_SM100A_V" + std::to_string(bsi_b200_version()); }
+
+// ---- additions (no counterpart in the reference module) -------------------------------------------
+// One call for a whole linear layer: pack x, dot with the keys, cast to x's dtype and add the bias.
+// Same arithmetic as BSIQuantizedLinear.forward (verify_accuracy_bsi.py:118-215) without the
+// capsule round trip, the float32 [Q, R] re-read by two elementwise kernels, or host syncs.
+at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c10::optional<torch::Tensor> bias,
+                              int decimalPlaces) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
+    PackedBatch qb = pack_queries(x2d, decimalPlaces);
+    py::tuple r = run_dot(qb, *keys, false, nullptr);
+    at::Tensor out = r[0].cast<at::Tensor>();
+    const int64_t Q = out.size(0), R = out.size(1);
+    at::ScalarType yt = x2d.scalar_type();
+    if (!(yt == at::kFloat || yt == at::kHalf || yt == at::kBFloat16)) yt = at::kFloat;
+    at::Tensor y = at::empty({Q, R}, out.options().dtype(yt));
+    const float* bptr = nullptr;
+    at::Tensor b32;
+    if (bias.has_value() && bias->defined()) {
+        b32 = bias->to(out.device(), at::kFloat).contiguous();
+        TORCH_CHECK(b32.numel() == R, "bias length mismatch");
+        bptr = b32.data_ptr<float>();
+    }
+    const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
+    check_status(bsi_b200_cast_bias(out.data_ptr<float>(), R, bptr, Q, R, y.data_ptr(), R, code, current_stream()),
+                 "bsi_b200_cast_bias");
+    return y;
+}
+
+py::dict debug_batch(const PackedBatch& b) {
+    py::dict d;
+    d["words"] = b.words;
+    d["slice_weights"] = b.slice_weights;
+    d["scales"] = b.scales;
+    d["q8"] = b.q8;
+    d["chunk_mode"] = b.chunk_mode;
+    d["S"] = b.S;
+    d["W"] = b.W;
+    d["decimals"] = b.decimals;
+    return d;
+}
+
+py::dict debug_query_batch_tensors(py::capsule cap) {
+    return debug_batch(from_capsule<PrebuiltBSIQueryBatchCUDA>(cap, "PrebuiltBSIQueryBatchCUDA")->b);
+}
+py::dict debug_keys_tensors(py::capsule cap) {
+    return debug_batch(from_capsule<PrebuiltBSIKeysCUDA>(cap, "PrebuiltBSIKeysCUDA")->b);
+}
+py::dict debug_query_tensors(py::capsule cap) {
+    auto* q = from_capsule<PrebuiltBSIQueryCUDA>(cap, "PrebuiltBSIQueryCUDA");
+    py::dict d;
+    d["words"] = q->parent->words[q->row];
+    d["slice_weights"] = q->parent->slice_weights[q->row];
+    d["scales"] = q->parent->scales[q->row];
+    d["twos_complement"] = q->twos_complement;
+    d["mem_bytes"] = q->mem_bytes;
+    return d;
+}
+
+// (out, int32 per-chunk accumulators [Q, R, chunks]) for the bit-exactness checks.
+py::tuple debug_dot_iacc(py::capsule query_batch_cap, py::capsule keyset_cuda_cap) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    auto* qb = from_capsule<PrebuiltBSIQueryBatchCUDA>(query_batch_cap, "PrebuiltBSIQueryBatchCUDA");
+    at::Tensor iacc;
+    py::tuple r = run_dot(qb->b, *keys, true, &iacc);
+    return py::make_tuple(r[0], iacc);
+}
+
+py::tuple ewah_encode_words(torch::Tensor words2d, double threshold) {
+    EwahStream e = ewah_encode(words2d, threshold);
+    return py::make_tuple(e.stream, e.off, e.len, e.flags);
+}
+
+at::Tensor ewah_decode_words(torch::Tensor stream, torch::Tensor off, torch::Tensor len, int64_t W) {
+    EwahStream e;
+    e.stream = stream.contiguous();
+    e.off = off.contiguous();
+    e.len = len.contiguous();
+    return ewah_decode(e, W);
+}
+
+int device_status() {
+    int v = 0;
+    check_status(bsi_b200_device_status(&v), "bsi_b200_device_status");
+    return v;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(bsi_ops, m) {
+    m.attr("CUDA_BUILDER_VERSION") = cuda_builder_version();
+    m.def("cuda_builder_version", &cuda_builder_version);
+    m.def("build_bsi_query_cuda", &build_bsi_query_cuda, py::arg("q"), py::arg("decimal_places"),
+          py::arg("compress_threshold") = 0.2f, "Build BSI query vector on CUDA");
+    m.def("build_bsi_queries_cuda_batch", &build_bsi_queries_cuda_batch, py::arg("q2d"), py::arg("decimal_places"),
+          py::arg("compress_threshold") = 0.2f, "Build BSI queries for a batch on CUDA");
+    m.def("build_bsi_queries_cuda_batch_packed", &build_bsi_queries_cuda_batch_packed, py::arg("q2d"),
+          py::arg("decimal_places"), py::arg("compress_threshold") = 0.2f,
+          "Build a packed (batched) BSI query object on CUDA (no per-row capsules)");
+    m.def("get_last_query_build_profile_cuda",
+          []() { return py::make_tuple(g_last_quantize_ns, g_last_pack_ns, g_last_total_ns); },
+          "Return (quantize_ns, pack_ns, total_ns) for the last CUDA query-batch build");
+    m.def("reset_last_query_build_profile_cuda", []() { g_last_quantize_ns = g_last_pack_ns = g_last_total_ns = 0; },
+          "Reset last CUDA query-batch build profile counters to zero");
+    m.def("build_bsi_query_cuda_hybrid", &build_bsi_query_cuda_hybrid, py::arg("q"), py::arg("decimal_places"),
+          py::arg("compress_threshold") = 0.2, "Build BSI query with EWAH compression");
+    m.def("batch_dot_product_multiquery_cuda_caps", &batch_dot_product_multiquery_cuda_caps,
+          py::arg("query_caps_list"), py::arg("keyset_cuda_cap"), "Multi-query batch dot product");
+    m.def("batch_dot_product_multiquery_cuda_batch_caps", &batch_dot_product_multiquery_cuda_batch_caps,
+          py::arg("query_batch_cap"), py::arg("keyset_cuda_cap"), "Packed-batch multi-query dot product");
+    m.def("bsi_keys_cuda_stats", &bsi_keys_cuda_stats, py::arg("keyset_cuda_cap"),
+          "Return shape/group stats for a CUDA BSI keyset");
+    m.def("bsi_query_caps_stats", &bsi_query_caps_stats, py::arg("query_caps_list"),
+          "Return shape stats for a list of CUDA BSI query capsules");
+    m.def("build_bsi_keys_cuda", &build_bsi_keys_cuda, py::arg("K"), py::arg("decimal_places"),
+          py::arg("compress_threshold") = 0.2f, "Build BSI keys and prepack to CUDA");
+
+    m.def("bsi_linear_forward", &bsi_linear_forward, py::arg("x2d"), py::arg("keyset_cuda_cap"),
+          py::arg("bias") = py::none(), py::arg("decimal_places") = 2,
+          "pack + dot + cast + bias for one linear layer");
+    m.def("debug_query_batch_tensors", &debug_query_batch_tensors);
+    m.def("debug_keys_tensors", &debug_keys_tensors);
+    m.def("debug_query_tensors", &debug_query_tensors);
+    m.def("debug_dot_iacc", &debug_dot_iacc);
+    m.def("ewah_encode_words", &ewah_encode_words, py::arg("words"), py::arg("threshold"));
+    m.def("ewah_decode_words", &ewah_decode_words, py::arg("stream"), py::arg("off"), py::arg("len"), py::arg("W"));
+    m.def("device_status", &device_status, "Read and clear the device-side timeout status word (synchronises)");
+}

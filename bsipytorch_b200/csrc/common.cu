@@ -1,0 +1,70 @@
+// Status strings, thread-local error text and device queries of the bsi_b200 library.
+#include "common.cuh"
+
+#include <stdarg.h>
+
+namespace bsi {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int require_sm100() {
+    static int cached[64] = {0};  // 0 unknown, 1 ok, 2 not sm_100
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        set_error("cudaGetDevice: %s", cudaGetErrorString(e));
+        return BSI_ERR_CUDA;
+    }
+    if (dev < 0 || dev >= 64) return BSI_OK;
+    if (cached[dev] == 0) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) {
+            set_error("cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+            return BSI_ERR_CUDA;
+        }
+        cached[dev] = (major == 10) ? 1 : 2;
+    }
+    if (cached[dev] != 1) {
+        set_error("bsi_b200 kernels are built for sm_100a only; current device is not compute capability 10.x");
+        return BSI_ERR_DEVICE;
+    }
+    return BSI_OK;
+}
+
+}  // namespace bsi
+
+extern "C" const char* bsi_b200_status_string(int status) {
+    switch (status) {
+        case BSI_OK: return "ok";
+        case BSI_ERR_INVALID: return "invalid argument";
+        case BSI_ERR_UNSUPPORTED: return "unsupported request";
+        case BSI_ERR_CUDA: return "CUDA call failed";
+        case BSI_ERR_DEVICE: return "not an sm_100 device";
+        case BSI_ERR_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+
+extern "C" const char* bsi_b200_last_error(void) { return bsi::g_err; }
+
+extern "C" int bsi_b200_version(void) { return BSI_B200_VERSION; }

@@ -1,0 +1,45 @@
+// Shared helpers of the bsi_b200 library: status codes, error recording, launch checks.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/bsi_b200.h"
+
+namespace bsi {
+
+// Thread-local detail of the last failure; read through bsi_b200_last_error().
+void set_error(const char* fmt, ...);
+
+inline int fail(int code, const char* what) {
+    set_error("%s", what);
+    return code;
+}
+
+// Checks the launch that was just enqueued (configuration errors surface here).
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("%s: %s", what, cudaGetErrorString(e));
+        return BSI_ERR_CUDA;
+    }
+    return BSI_OK;
+}
+
+#define BSI_CUDA_TRY(expr)                                                        \
+    do {                                                                          \
+        cudaError_t _e = (expr);                                                  \
+        if (_e != cudaSuccess) {                                                  \
+            ::bsi::set_error("%s: %s", #expr, cudaGetErrorString(_e));            \
+            return BSI_ERR_CUDA;                                                  \
+        }                                                                         \
+    } while (0)
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// 0 when the current device is sm_100 class, an error code otherwise.
+int require_sm100();
+
+}  // namespace bsi

@@ -1,0 +1,360 @@
+// EWAH / verbatim slice encoder and decoder.
+//
+// The reference encodes each slice with ONE thread walking the words in order
+// (bsi_cuda_kernels_ewah.cuh:118-162 size, :178-232 emit). The same stream is produced here by
+// one WARP per slice with ballots and prefix counts:
+//   type(w)     = zero-fill (word == 0), one-fill (word == ~0) or literal; with the compress
+//                 flag clear every word is a literal
+//   start(w)    = w == 0, or word w is a fill word whose type differs from word w-1
+//                 (a segment is: an optional run of one fill word, then literals up to the
+//                 next fill word)
+//   RLW position of the k-th segment (k from 0) = k + literals before its first word
+//   literal w goes to (segments started at or before w) + (literals before w)
+//   RLW = run_bit | (run_len & 0xFFFFFFFF) << 1 | literal_count << 33, written when the segment
+//   closes (at the next start, or at W).
+#include "common.cuh"
+
+namespace bsi {
+namespace {
+
+typedef unsigned long long u64;
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ u64 warp_sum_u64(u64 v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+__device__ __forceinline__ int compress_flag(u64 count, int64_t W, double threshold) {
+    // Same expressions as bsi_cuda_kernels_ewah.cuh:94-101 so that pow() rounds identically.
+    const double total_bits = static_cast<double>(W) * 64.0;
+    double p = (total_bits > 0.0) ? (static_cast<double>(count) / total_bits) : 0.0;
+    if (p < 0.0) p = 0.0;
+    if (p > 1.0) p = 1.0;
+    const double a = pow(1.0 - p, 128.0);
+    const double b = pow(p, 128.0);
+    const double M = 1.0 - a - b;
+    return (M <= threshold) ? 1 : 0;
+}
+
+// Walks one slice with a warp. EMIT=false only counts; EMIT=true also writes the stream.
+template <bool EMIT>
+__device__ __forceinline__ u64 encode_slice(const u64* __restrict__ base, int64_t W, int compress,
+                                            u64* __restrict__ out, int lane) {
+    if (!compress) {
+        if (EMIT) {
+            if (lane == 0) out[0] = static_cast<u64>(W) << 33;
+            for (int64_t w = lane; w < W; w += 32) out[1 + w] = base[w];
+        }
+        return 1ull + static_cast<u64>(W);
+    }
+    const unsigned below = (1u << lane) - 1u;
+    u64 seg_base = 0;  // segments started before this tile
+    u64 lit_base = 0;  // literals before this tile
+    int prev_type = 2; // type of the last word of the previous tile
+    // The open segment (valid once seg_base > 0): first word, literals before it, its fill bit.
+    int64_t open_w0 = 0;
+    u64 open_lit0 = 0;
+    int open_bit = 0;
+    int open_isfill = 0;
+
+    for (int64_t tile = 0; tile < W; tile += 32) {
+        const int64_t w = tile + lane;
+        const bool valid = w < W;
+        const u64 word = valid ? base[w] : 1ull;  // padding lanes look like literals, never counted
+        const int type = (word == 0ull) ? 0 : ((word == ~0ull) ? 1 : 2);
+        int left = __shfl_up_sync(0xffffffffu, type, 1);
+        if (lane == 0) left = prev_type;
+        const bool start = valid && (w == 0 || (type != 2 && type != left));
+        const bool lit = valid && type == 2;
+        const unsigned S = __ballot_sync(0xffffffffu, start);
+        const unsigned L = __ballot_sync(0xffffffffu, lit);
+
+        if (EMIT) {
+            const u64 lit_here = lit_base + __popc(L & below);
+            if (lit) {
+                const u64 segs_incl = seg_base + __popc(S & (below | (1u << lane)));
+                out[segs_incl + lit_here] = word;
+            }
+            // A start at w (other than the very first word) closes the segment before it.
+            const unsigned prior = S & below;
+            const int p = prior ? (31 - __clz(prior)) : 0;
+            const int p_type = __shfl_sync(0xffffffffu, type, p);
+            if (start && w != 0) {
+                int64_t w0;
+                u64 lit0, pos;
+                int bit, isfill;
+                if (prior) {
+                    w0 = tile + p;
+                    lit0 = lit_base + __popc(L & ((1u << p) - 1u));
+                    pos = seg_base + __popc(S & ((1u << p) - 1u)) + lit0;
+                    bit = (p_type == 1);
+                    isfill = (p_type != 2);
+                } else {
+                    w0 = open_w0;
+                    lit0 = open_lit0;
+                    pos = (seg_base - 1) + lit0;
+                    bit = open_bit;
+                    isfill = open_isfill;
+                }
+                const u64 lit_count = lit_here - lit0;
+                const u64 run_len = isfill ? (static_cast<u64>(w - w0) - lit_count) : 0ull;
+                out[pos] = static_cast<u64>(bit) | ((run_len & 0xFFFFFFFFull) << 1) | (lit_count << 33);
+            }
+        }
+        // Carry the last start of this tile forward as the open segment.
+        if (S) {
+            const int p = 31 - __clz(S);
+            const int p_type = __shfl_sync(0xffffffffu, type, p);
+            open_w0 = tile + p;
+            open_lit0 = lit_base + __popc(L & ((1u << p) - 1u));
+            open_bit = (p_type == 1);
+            open_isfill = (p_type != 2);
+        }
+        seg_base += __popc(S);
+        lit_base += __popc(L);
+        const int last = (W - tile) >= 32 ? 31 : static_cast<int>(W - tile - 1);
+        prev_type = __shfl_sync(0xffffffffu, type, last);
+    }
+    if (EMIT && lane == 0 && seg_base > 0) {
+        const u64 lit_count = lit_base - open_lit0;
+        const u64 run_len = open_isfill ? (static_cast<u64>(W - open_w0) - lit_count) : 0ull;
+        out[(seg_base - 1) + open_lit0] =
+            static_cast<u64>(open_bit) | ((run_len & 0xFFFFFFFFull) << 1) | (lit_count << 33);
+    }
+    return seg_base + lit_base;
+}
+
+// counts/flags and (optionally) sizes in one pass over the words.
+template <bool WITH_SIZE>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_flags_kernel(
+    const u64* __restrict__ words, int64_t S, int64_t W, double threshold,
+    u64* __restrict__ counts, int32_t* __restrict__ flags, u64* __restrict__ sizes) {
+    const int lane = threadIdx.x & 31;
+    const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (s >= S) return;
+    const u64* base = words + s * W;
+    u64 local = 0;
+    for (int64_t w = lane; w < W; w += 32) local += static_cast<u64>(__popcll(base[w]));
+    const u64 count = warp_sum_u64(local);
+    const int flag = compress_flag(count, W, threshold);
+    if (lane == 0) {
+        if (counts != nullptr) counts[s] = count;
+        flags[s] = flag;
+    }
+    if (WITH_SIZE) {
+        const u64 n = encode_slice<false>(base, W, flag, nullptr, lane);
+        if (lane == 0) sizes[s] = n;
+    }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_size_kernel(
+    const u64* __restrict__ words, int64_t S, int64_t W, const int32_t* __restrict__ flags,
+    u64* __restrict__ sizes) {
+    const int lane = threadIdx.x & 31;
+    const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (s >= S) return;
+    const u64 n = encode_slice<false>(words + s * W, W, flags[s], nullptr, lane);
+    if (lane == 0) sizes[s] = n;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_kernel(
+    const u64* __restrict__ words, int64_t S, int64_t W, const int32_t* __restrict__ flags,
+    const u64* __restrict__ off, const u64* __restrict__ sizes, u64 capacity,
+    u64* __restrict__ out, int32_t* __restrict__ out_len) {
+    const int lane = threadIdx.x & 31;
+    const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (s >= S) return;
+    const u64 o = off[s];
+    if (sizes != nullptr && o + sizes[s] > capacity) {
+        if (lane == 0) out_len[s] = static_cast<int32_t>(sizes[s]);
+        return;
+    }
+    const u64 n = encode_slice<true>(words + s * W, W, flags[s], out + o, lane);
+    if (lane == 0) out_len[s] = static_cast<int32_t>(n);
+}
+
+// Exclusive prefix sum with one block; S is at most a few hundred thousand slices.
+__global__ void __launch_bounds__(1024) ewah_offsets_kernel(const u64* __restrict__ sizes, int64_t S,
+                                                            u64* __restrict__ off,
+                                                            u64* __restrict__ total) {
+    __shared__ u64 warp_tot[32];
+    __shared__ u64 carry;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    for (int64_t tile = 0; tile < S; tile += 1024) {
+        const int64_t i = tile + threadIdx.x;
+        const u64 v = i < S ? sizes[i] : 0ull;
+        u64 incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const u64 t = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += t;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            u64 t = warp_tot[lane];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const u64 u = __shfl_up_sync(0xffffffffu, t, d);
+                if (lane >= d) t += u;
+            }
+            warp_tot[lane] = t;
+        }
+        __syncthreads();
+        const u64 before = carry + (warp ? warp_tot[warp - 1] : 0ull) + (incl - v);
+        if (i < S) off[i] = before;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = before + v;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && total != nullptr) *total = carry;
+}
+
+// Decode: lane 0 parses the RLWs in order (bsi_cuda_kernels_ewah.cuh:16-32), the warp fills runs
+// and copies literals together.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_decode_kernel(
+    const u64* __restrict__ in, const u64* __restrict__ off, const int32_t* __restrict__ len,
+    int64_t S, int64_t W, u64* __restrict__ out) {
+    const int lane = threadIdx.x & 31;
+    const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + (threadIdx.x >> 5);
+    if (s >= S) return;
+    const u64* src = in + off[s];
+    const int64_t in_len = len[s];
+    u64* dst = out + s * W;
+    int64_t idx = 0, o = 0;
+    while (idx < in_len && o < W) {
+        const u64 rlw = src[idx++];
+        const u64 run_val = (rlw & 1ull) ? ~0ull : 0ull;
+        int64_t run_len = static_cast<int64_t>((rlw >> 1) & 0xFFFFFFFFull);
+        int64_t lit = static_cast<int64_t>(rlw >> 33);
+        if (run_len > W - o) run_len = W - o;
+        for (int64_t k = lane; k < run_len; k += 32) dst[o + k] = run_val;
+        o += run_len;
+        if (lit > W - o) lit = W - o;
+        if (lit > in_len - idx) lit = in_len - idx;
+        for (int64_t k = lane; k < lit; k += 32) dst[o + k] = src[idx + k];
+        o += lit;
+        idx += lit;
+    }
+    for (int64_t k = o + lane; k < W; k += 32) dst[k] = 0ull;
+}
+
+inline unsigned warp_blocks(int64_t S) { return static_cast<unsigned>((S + kWarpsPerBlock - 1) / kWarpsPerBlock); }
+
+int check_sw(const char* name, const void* words, int64_t S, int64_t W) {
+    if (S < 0 || W <= 0) {
+        set_error("%s: bad S/W", name);
+        return BSI_ERR_INVALID;
+    }
+    if (S > 0 && words == nullptr) {
+        set_error("%s: words is null", name);
+        return BSI_ERR_INVALID;
+    }
+    if ((S + kWarpsPerBlock - 1) / kWarpsPerBlock > 0x7fffffffll) {
+        set_error("%s: too many slices for one launch", name);
+        return BSI_ERR_UNSUPPORTED;
+    }
+    return require_sm100();
+}
+
+}  // namespace
+}  // namespace bsi
+
+using bsi::u64;
+
+extern "C" int bsi_b200_ewah_flags(const uint64_t* words, int64_t S, int64_t W, double threshold,
+                                   uint64_t* counts, int32_t* flags, bsi_stream_t stream_) {
+    using namespace bsi;
+    if (int rc = check_sw("ewah_flags", words, S, W)) return rc;
+    if (S == 0) return BSI_OK;
+    if (flags == nullptr) return fail(BSI_ERR_INVALID, "ewah_flags: flags is null");
+    ewah_flags_kernel<false><<<warp_blocks(S), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+        reinterpret_cast<const u64*>(words), S, W, threshold, reinterpret_cast<u64*>(counts), flags, nullptr);
+    return check_launch("ewah_flags launch");
+}
+
+extern "C" int bsi_b200_ewah_size(const uint64_t* words, int64_t S, int64_t W, const int32_t* flags,
+                                  uint64_t* sizes, bsi_stream_t stream_) {
+    using namespace bsi;
+    if (int rc = check_sw("ewah_size", words, S, W)) return rc;
+    if (S == 0) return BSI_OK;
+    if (flags == nullptr || sizes == nullptr) return fail(BSI_ERR_INVALID, "ewah_size: null pointer");
+    ewah_size_kernel<<<warp_blocks(S), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+        reinterpret_cast<const u64*>(words), S, W, flags, reinterpret_cast<u64*>(sizes));
+    return check_launch("ewah_size launch");
+}
+
+extern "C" int bsi_b200_ewah_offsets(const uint64_t* sizes, int64_t S, uint64_t* off, uint64_t* total,
+                                     bsi_stream_t stream_) {
+    using namespace bsi;
+    if (S < 0) return fail(BSI_ERR_INVALID, "ewah_offsets: bad S");
+    if (S > 0 && (sizes == nullptr || off == nullptr)) return fail(BSI_ERR_INVALID, "ewah_offsets: null pointer");
+    if (int rc = require_sm100()) return rc;
+    ewah_offsets_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream_)>>>(
+        reinterpret_cast<const u64*>(sizes), S, reinterpret_cast<u64*>(off), reinterpret_cast<u64*>(total));
+    return check_launch("ewah_offsets launch");
+}
+
+extern "C" int bsi_b200_ewah_emit(const uint64_t* words, int64_t S, int64_t W, const int32_t* flags,
+                                  const uint64_t* off, uint64_t* out, int32_t* out_len,
+                                  bsi_stream_t stream_) {
+    using namespace bsi;
+    if (int rc = check_sw("ewah_emit", words, S, W)) return rc;
+    if (S == 0) return BSI_OK;
+    if (flags == nullptr || off == nullptr || out == nullptr || out_len == nullptr)
+        return fail(BSI_ERR_INVALID, "ewah_emit: null pointer");
+    ewah_emit_kernel<<<warp_blocks(S), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+        reinterpret_cast<const u64*>(words), S, W, flags, reinterpret_cast<const u64*>(off), nullptr, 0ull,
+        reinterpret_cast<u64*>(out), out_len);
+    return check_launch("ewah_emit launch");
+}
+
+extern "C" int bsi_b200_ewah_decode(const uint64_t* in, const uint64_t* off, const int32_t* len,
+                                    int64_t S, int64_t W, uint64_t* out, bsi_stream_t stream_) {
+    using namespace bsi;
+    if (int rc = check_sw("ewah_decode", in, S, W)) return rc;
+    if (S == 0) return BSI_OK;
+    if (off == nullptr || len == nullptr || out == nullptr) return fail(BSI_ERR_INVALID, "ewah_decode: null pointer");
+    ewah_decode_kernel<<<warp_blocks(S), kWarpsPerBlock * 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+        reinterpret_cast<const u64*>(in), reinterpret_cast<const u64*>(off), len, S, W,
+        reinterpret_cast<u64*>(out));
+    return check_launch("ewah_decode launch");
+}
+
+extern "C" int64_t bsi_b200_ewah_scratch_bytes(int64_t S) {
+    // counts [S] + sizes [S], both uint64.
+    return S < 0 ? 0 : 2 * S * static_cast<int64_t>(sizeof(uint64_t));
+}
+
+extern "C" int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W, double threshold,
+                                    void* scratch, int64_t scratch_bytes,
+                                    uint64_t* out, int64_t capacity, uint64_t* off, int32_t* out_len,
+                                    int32_t* flags, uint64_t* total, bsi_stream_t stream_) {
+    using namespace bsi;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (int rc = check_sw("ewah_encode", words, S, W)) return rc;
+    if (S == 0) return BSI_OK;
+    if (scratch == nullptr || scratch_bytes < bsi_b200_ewah_scratch_bytes(S) ||
+        (reinterpret_cast<uintptr_t>(scratch) & 7) != 0)
+        return fail(BSI_ERR_INVALID, "ewah_encode: scratch too small or misaligned");
+    if (out == nullptr || off == nullptr || out_len == nullptr || flags == nullptr || capacity < 0)
+        return fail(BSI_ERR_INVALID, "ewah_encode: null pointer");
+    u64* counts = static_cast<u64*>(scratch);
+    u64* sizes = counts + S;
+    ewah_flags_kernel<true><<<warp_blocks(S), kWarpsPerBlock * 32, 0, stream>>>(
+        reinterpret_cast<const u64*>(words), S, W, threshold, counts, flags, sizes);
+    if (int rc = check_launch("ewah_encode flags launch")) return rc;
+    ewah_offsets_kernel<<<1, 1024, 0, stream>>>(sizes, S, reinterpret_cast<u64*>(off),
+                                               reinterpret_cast<u64*>(total));
+    if (int rc = check_launch("ewah_encode offsets launch")) return rc;
+    ewah_emit_kernel<<<warp_blocks(S), kWarpsPerBlock * 32, 0, stream>>>(
+        reinterpret_cast<const u64*>(words), S, W, flags, reinterpret_cast<const u64*>(off), sizes,
+        static_cast<u64>(capacity), reinterpret_cast<u64*>(out), out_len);
+    return check_launch("ewah_encode emit launch");
+}

@@ -1,0 +1,164 @@
+/*
+ * bsi_b200 -- C ABI of the B200 (sm_100a) bit-sliced-index (BSI) tensor-dot library.
+ *
+ * Plain pointers and sizes only; no torch types. Every pointer is a DEVICE pointer unless
+ * the comment says "host". Every function enqueues its work on `stream` (a cudaStream_t)
+ * of the CURRENT device and returns without synchronising, unless stated otherwise.
+ * The caller owns all memory. Return value: 0 on success, a BSI_ERR_* code otherwise;
+ * bsi_b200_last_error() gives the detail of the last failure on the calling thread.
+ *
+ * Each entry point names the interface of the reference (gguzunsjsu/bsiPytorch, paths
+ * relative to its checkout) that it replaces.
+ *
+ * Layouts (row-major, same as the reference):
+ *   words   [rows, S, W]  uint64, W = ceil(D/64); bit t of word w of slice s is bit s of the
+ *                         two's-complement value of element 64*w + t (zero beyond D)
+ *   scales  [rows, chunks] float32 (chunk mode, chunks = ceil(D/256)) or [rows] (row mode):
+ *                         2^shift of each 256-element chunk / each row
+ *   q8      [rows, ld8]   int8, the clamped integers, zero padded to ld8 >= 256*chunks
+ *   out     [Q, ldo]      float32
+ */
+#ifndef BSI_B200_H_
+#define BSI_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSI_B200_VERSION 100
+
+enum {
+    BSI_OK = 0,
+    BSI_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, misaligned buffer) */
+    BSI_ERR_UNSUPPORTED = 2, /* valid request that this build does not implement */
+    BSI_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed */
+    BSI_ERR_DEVICE = 4,      /* not an sm_100 device */
+    BSI_ERR_TIMEOUT = 5      /* a bounded device-side wait ran out (see bsi_b200_device_status) */
+};
+
+/* Input element types; the same codes the reference's launchers use
+ * (bsi_vector_cuda.cpp:353-358). */
+enum { BSI_DTYPE_F32 = 0, BSI_DTYPE_F16 = 1, BSI_DTYPE_BF16 = 2 };
+
+/* Dot engines. */
+enum {
+    BSI_ENGINE_AUTO = 0,    /* tcgen05 */
+    BSI_ENGINE_TCGEN05 = 1, /* int8 recombination, tcgen05.mma kind::i8, TMEM accumulators, TMA */
+    BSI_ENGINE_SIMT = 2,    /* dp4a on the CUDA cores (cross-check engine) */
+    BSI_ENGINE_BMMA = 3     /* mma.sync b1 AND+POPC directly on the slice words */
+};
+
+typedef void* bsi_stream_t; /* cudaStream_t */
+
+const char* bsi_b200_status_string(int status);
+const char* bsi_b200_last_error(void);
+int bsi_b200_version(void);
+
+/* Reads (and clears) the device-side status word that kernels set when one of their bounded
+ * waits gives up. Synchronises the device. *status_out (host): 0 = clean. */
+int bsi_b200_device_status(int* status_out);
+
+/* ---- quantise + bit-slice pack -------------------------------------------------------
+ * One pass over x: v = half_away(double(float(x)) * 10^decimal_places); shift from the
+ * largest |v| of each 256-element chunk (chunk_mode=1) or each row (chunk_mode=0);
+ * q = round-shift, clamp to `bits`-bit two's complement; writes bit slices, 2^shift
+ * scales and (optionally) the int8 image. Any of words/scales/shifts/q8 may be NULL.
+ *
+ * Replaces, for queries (chunk_mode=1): launch_compute_chunk_shift_scale_from_input +
+ * launch_quantize_shift_pack_chunk_batch (bsi_cuda_kernels_quant.cuh:524-557, 596-636) and
+ * the zero-fill before them (bsi_vector_cuda.cpp:427); for keys and the row-scale mode
+ * (chunk_mode=0): launch_quantize_round_to_int64_batch + launch_compute_row_shift_scale +
+ * launch_apply_row_shift_clamp + launch_pack_bits_all_ballot_batch
+ * (bsi_cuda_kernels_quant.cuh:638-716, bsi_cuda_kernels_pack.cuh:204-230) and
+ * launch_compute_row_shift_scale_from_input + launch_quantize_shift_pack_row_batch
+ * (bsi_cuda_kernels_quant.cuh:490-522, 559-594).
+ *
+ * x: [rows, D] with row stride ldx (elements). bits in [2, 8]. ld8: row stride of q8 in
+ * bytes (>= 256*ceil(D/256), multiple of 16); columns D..ld8-1 are written as zero. */
+int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                           int decimal_places, int bits, int chunk_mode,
+                           uint64_t* words, float* scales, int32_t* shifts,
+                           int8_t* q8, int64_t ld8, bsi_stream_t stream);
+
+/* Slice words -> int8 image (sign-extends the top slice). Used when a caller holds only the
+ * bit slices (e.g. words built by the reference). No counterpart in the reference, whose dot
+ * consumes the slices directly (bsi_cuda_kernels_dot.cuh:1436-1517). */
+int bsi_b200_recombine_i8(const uint64_t* words, int64_t rows, int bits, int64_t W,
+                          int8_t* q8, int64_t ld8, bsi_stream_t stream);
+
+/* ---- dot core ------------------------------------------------------------------------
+ * out[q][r] = ( sum over chunks c, ascending, each step rounded to float32, of
+ *               float(I[q][r][c]) * qs[q][c] * bw0[r] ) * scale_inv,
+ * I[q][r][c] = sum_{d in chunk c} a8[q][d] * k8[r][d]   (int32, exact; equals the weighted
+ * popcount sum over the slice pairs). qs_stride = chunks for chunk scales, 0 for one scale per
+ * row. dbg_iacc (optional, [Q, R, chunks] int32) receives I.
+ *
+ * Replaces launch_popcount_weighted_keys_literal_fused_multiq in its fixed-bit modes
+ * (bsi_cuda_kernels_dot.cuh:2616-3090; kernels :1285-1556, :1558-1920, :1922-2307).
+ * a8/k8 rows must be 16-byte aligned with lda/ldk multiples of 16 and >= 256*chunks. */
+int bsi_b200_dot_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                    const int8_t* k8, int64_t ldk, const float* bw0,
+                    int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                    float* out, int64_t ldo, int32_t* dbg_iacc, int engine,
+                    bsi_stream_t stream);
+
+/* Same result computed from the slice words with mma.sync b1 AND+POPC, argument order of the
+ * reference launcher (bsi_cuda_kernels_dot.cuh:2616-2635) minus the tile hints and index
+ * arrays. Bw is [R, Sb]; only Bw[r][0] = 2^shift_r enters (the slice weights are +-2^j * Bw[r][0],
+ * bsi_vector_cuda.cpp:1148-1157). Requires W % 4 == 0, Sa <= 8, Sb <= 8. */
+int bsi_b200_dot_words(const uint64_t* A, const float* qs, int64_t qs_stride, int Sa, int64_t W,
+                       const uint64_t* B, const float* Bw, int Sb, int64_t R, int64_t Q,
+                       float scale_inv, int64_t ldo, float* out, int32_t* dbg_iacc,
+                       bsi_stream_t stream);
+
+/* ---- EWAH / verbatim slice encoder ---------------------------------------------------
+ * words [S, W] (S = any number of slices, e.g. rows*bits).
+ * flags: p = popcount/(64 W); M = 1 - (1-p)^128 - p^128 (float64); compress = (M <= threshold).
+ * Replaces launch_slice_popcount_sum + launch_compress_flags_from_density
+ * (bsi_cuda_kernels_ewah.cuh:71-81, 104-115). counts may be NULL. */
+int bsi_b200_ewah_flags(const uint64_t* words, int64_t S, int64_t W, double threshold,
+                        uint64_t* counts, int32_t* flags, bsi_stream_t stream);
+
+/* Number of uint64 each slice encodes to. Replaces launch_ewah_size (ewah.cuh:164-175). */
+int bsi_b200_ewah_size(const uint64_t* words, int64_t S, int64_t W, const int32_t* flags,
+                       uint64_t* sizes, bsi_stream_t stream);
+
+/* Exclusive prefix sum of sizes -> off [S]; total (device, 1 element) = sum. Replaces the
+ * cumsum glue of bsi_vector_cuda.cpp:929-939. */
+int bsi_b200_ewah_offsets(const uint64_t* sizes, int64_t S, uint64_t* off, uint64_t* total,
+                          bsi_stream_t stream);
+
+/* Writes [RLW, literals...]* per slice at out + off[s]; out_len[s] = words written.
+ * RLW = run_bit | (run_len & 0xFFFFFFFF) << 1 | literal_count << 33.
+ * Replaces launch_ewah_emit (ewah.cuh:234-247); identical streams. */
+int bsi_b200_ewah_emit(const uint64_t* words, int64_t S, int64_t W, const int32_t* flags,
+                       const uint64_t* off, uint64_t* out, int32_t* out_len, bsi_stream_t stream);
+
+/* Decodes S streams (in + off[s], len[s] words) into out [S, W], zero padded.
+ * Replaces the per-slice launch_ewah_decompress loop (ewah.cuh:35-42, bsi_cuda.cpp:402-414). */
+int bsi_b200_ewah_decode(const uint64_t* in, const uint64_t* off, const int32_t* len,
+                         int64_t S, int64_t W, uint64_t* out, bsi_stream_t stream);
+
+/* One call: flags -> sizes -> offsets -> emit. scratch: device buffer of at least
+ * bsi_b200_ewah_scratch_bytes(S) bytes. capacity: uint64 slots available at out; a stream that
+ * would exceed it is not written and *total (device) still reports the needed size.
+ * Replaces build_bsi_vector_from_float_tensor_hybrid's encode half (bsi_vector_cuda.cpp:900-952). */
+int64_t bsi_b200_ewah_scratch_bytes(int64_t S);
+int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W, double threshold,
+                         void* scratch, int64_t scratch_bytes,
+                         uint64_t* out, int64_t capacity, uint64_t* off, int32_t* out_len,
+                         int32_t* flags, uint64_t* total, bsi_stream_t stream);
+
+/* ---- layer epilogue ------------------------------------------------------------------
+ * y[q][r] = cast(out[q][r]) + cast(bias[r]) in y_dtype (BSI_DTYPE_*), one pass.
+ * Replaces the two torch elementwise kernels of BSIQuantizedLinear.forward
+ * (bsi_ops/benchmarks/verify_accuracy_bsi.py:193-195). bias may be NULL. */
+int bsi_b200_cast_bias(const float* out, int64_t ldo, const float* bias, int64_t Q, int64_t R,
+                       void* y, int64_t ldy, int y_dtype, bsi_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSI_B200_H_ */
