@@ -1,0 +1,165 @@
+"""Dot core, through the C ABI: every engine against the CPU checker, bit-exact.
+
+Integer per-chunk accumulators must equal the weighted popcount sum exactly; float32 outputs are
+compared bit for bit as well (tolerance the task allows: rtol 1e-5 / atol 1e-6 -- we ask for zero).
+"""
+import numpy as np
+import pytest
+import torch
+
+import _capi_helpers as H
+import _inputs
+from bsipytorch_b200 import capi
+from oracle import oracle as o
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ENGINES = {"simt": capi.ENGINE_SIMT, "tcgen05": capi.ENGINE_TCGEN05, "tcgen05_bn64": 1064,
+           "tcgen05_bn128": 1128, "tcgen05_bn256": 1256}
+
+
+def _prepare(q, k, bits_q=7, bits_k=6, chunk_mode=True, dp=2):
+    qa = H.quantize_pack(q.to(DEV), dp, bits_q, chunk_mode)
+    kb = H.quantize_pack(k.to(DEV), dp, bits_k, False)
+    Bw = torch.from_numpy(o.slice_weights(bits_k, kb["scales"].cpu().numpy())).to(DEV)
+    return qa, kb, Bw
+
+
+def _oracle(q, k, bits_q=7, bits_k=6, chunk_mode=True, dp=2):
+    qa = o.quantize_pack(q.float().numpy(), dp, bits_q, chunk_mode)
+    kb = o.quantize_pack(k.float().numpy(), dp, bits_k, False)
+    chunks = (q.shape[1] + 255) // 256
+    return o.dot_i8(o.pad_i8(qa["qvals"], chunks), qa["scales"], o.pad_i8(kb["qvals"], chunks),
+                    kb["scales"], o.scale_inv(dp), want_iacc=True)
+
+
+def _assert_bits(got, want):
+    np.testing.assert_array_equal(got.cpu().numpy().view(np.uint32), want.view(np.uint32))
+
+
+SHAPES = [(64, 256, 2048), (70, 100, 512), (200, 300, 1024), (128, 256, 256), (1, 1, 256), (130, 513, 768),
+          (33, 65, 250)]
+
+
+@pytest.mark.parametrize("engine", list(ENGINES))
+@pytest.mark.parametrize("shape", SHAPES)
+def test_dot_i8_engines_match_oracle(engine, shape):
+    Q, R, D = shape
+    q, k = _inputs.fc1(Q=Q, R=R, D=D, seed=Q + R + D, dtype=torch.float32)
+    qa, kb, _ = _prepare(q, k)
+    out, iacc = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), ENGINES[engine], True)
+    want, want_i = _oracle(q, k)
+    np.testing.assert_array_equal(iacc.cpu().numpy(), want_i)
+    _assert_bits(out, want)
+    # the same call without the debug output
+    out2 = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), ENGINES[engine], False)
+    assert torch.equal(out, out2)
+    assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(64, 256, 2048), (70, 100, 512), (96, 160, 1024)])
+def test_dot_words_bmma_matches_oracle(shape):
+    Q, R, D = shape
+    q, k = _inputs.fc1(Q=Q, R=R, D=D, seed=11 + Q, dtype=torch.float16)
+    qa, kb, Bw = _prepare(q, k)
+    out, iacc = H.dot_words(qa["words"], qa["scales"], kb["words"], Bw, o.scale_inv(2), True)
+    want, want_i = _oracle(q, k)
+    np.testing.assert_array_equal(iacc.cpu().numpy(), want_i)
+    _assert_bits(out, want)
+    # and the weighted-popcount form of the checker on the same words
+    pop = o.dot_popc(H.as_u64(qa["words"]), qa["scales"].cpu().numpy(), H.as_u64(kb["words"]), Bw.cpu().numpy(),
+                     o.scale_inv(2))
+    _assert_bits(out, pop)
+
+
+@pytest.mark.parametrize("engine", ["simt", "tcgen05"])
+def test_dot_row_scale_mode(engine):
+    # one scale per query row (qs_stride = 0): the mode used when the word count is not a multiple of 4
+    q, k = _inputs.c1(Q=40, R=72, D=320)
+    qa, kb, _ = _prepare(q, k, chunk_mode=False)
+    out, iacc = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), ENGINES[engine], True)
+    want, want_i = _oracle(q, k, chunk_mode=False)
+    np.testing.assert_array_equal(iacc.cpu().numpy(), want_i)
+    _assert_bits(out, want)
+
+
+@pytest.mark.parametrize("bits", [(8, 8), (4, 4), (7, 7), (2, 3)])
+def test_dot_other_slice_counts(bits):
+    bq, bk = bits
+    q, k = _inputs.c1(Q=48, R=80, D=512, seed=bq * 10 + bk)
+    qa, kb, Bw = _prepare(q, k, bq, bk)
+    want, want_i = _oracle(q, k, bq, bk)
+    out, iacc = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), capi.ENGINE_TCGEN05, True)
+    np.testing.assert_array_equal(iacc.cpu().numpy(), want_i)
+    _assert_bits(out, want)
+    if bits in [(8, 8), (4, 4), (7, 7)]:
+        out_b = H.dot_words(qa["words"], qa["scales"], kb["words"], Bw, o.scale_inv(2))
+        _assert_bits(out_b, want)
+
+
+def test_dot_extreme_accumulators():
+    # every query element +63 / -64 and every key element -32 / +31: |I| reaches 256*64*32 = 2^19
+    Q, R, D = 32, 32, 512
+    q = torch.full((Q, D), 0.63)
+    q[1::2] = -0.64 * 1.0
+    q[1::2, 0] = -0.63      # keep max |v| at 64 -> shift 1 for odd rows; even rows shift 0
+    k = torch.full((R, D), 0.31)
+    k[1::2] = -0.31
+    qa, kb, _ = _prepare(q, k)
+    want, want_i = _oracle(q, k)
+    for engine in ("simt", "tcgen05"):
+        out, iacc = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), ENGINES[engine], True)
+        np.testing.assert_array_equal(iacc.cpu().numpy(), want_i)
+        _assert_bits(out, want)
+    assert np.abs(want_i).max() >= 256 * 63 * 31
+
+
+def test_dot_matches_reference_kernels():
+    """The reference's fixed76 chunk-scale kernels (rsweep4 + tail) on the same packed operands."""
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("reference kernels not built on this machine")
+    for (Q, R, D) in [(64, 256, 2048), (96, 160, 1024), (128, 512, 4096)]:
+        q, k = _inputs.fc1(Q=Q, R=R, D=D, seed=Q)
+        qa, kb, Bw = _prepare(q, k)
+        ref = ref_gpu.dot_fixed76(qa["words"], qa["scales"], kb["words"], Bw, o.scale_inv(2))
+        for engine in ("simt", "tcgen05"):
+            out = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), ENGINES[engine])
+            assert torch.equal(out, ref), engine
+        assert torch.equal(H.dot_words(qa["words"], qa["scales"], kb["words"], Bw, o.scale_inv(2)), ref)
+
+
+@pytest.mark.parametrize("cfg", ["fc1", "fc2"])
+def test_dot_full_size_configs(cfg):
+    """BASELINE sizes: engines agree bit for bit with each other, and with the checker on a row sample."""
+    q, k = (_inputs.fc1() if cfg == "fc1" else _inputs.fc2())
+    qa, kb, Bw = _prepare(q, k)
+    si = o.scale_inv(2)
+    out_tc = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], si, capi.ENGINE_TCGEN05)
+    out_simt = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], si, capi.ENGINE_SIMT)
+    assert torch.equal(out_tc, out_simt)
+    out_bmma = H.dot_words(qa["words"], qa["scales"], kb["words"], Bw, si)
+    assert torch.equal(out_tc, out_bmma)
+    rows = torch.arange(0, q.shape[0], 37)
+    want, _ = _oracle(q[rows], k)
+    _assert_bits(out_tc[rows.to(DEV)], want)
+    # linearity in the integer domain: doubling a key row's scale doubles that output column exactly
+    bw2 = kb["scales"].clone()
+    bw2[5] *= 2
+    out2 = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], bw2, si, capi.ENGINE_TCGEN05)
+    assert torch.equal(out2[:, 5], out_tc[:, 5] * 2) and torch.equal(out2[:, 6:], out_tc[:, 6:])
+    assert capi.device_status() == 0
+
+
+def test_dot_bad_arguments():
+    L = capi.lib()
+    a = torch.zeros(4, 256, dtype=torch.int8, device=DEV)
+    f = torch.ones(4, 1, device=DEV)
+    out = torch.zeros(4, 4, device=DEV)
+    import ctypes as C
+    args = lambda lda, ldo, eng: (capi.ptr(a), lda, capi.ptr(f), 1, capi.ptr(a), 256, capi.ptr(f), 4, 4, 1,
+                                   C.c_float(1.0), capi.ptr(out), ldo, None, eng, None)
+    assert L.bsi_b200_dot_i8(*args(128, 4, 0)) == capi.ERR_INVALID      # lda < 256 * chunks
+    assert L.bsi_b200_dot_i8(*args(256, 2, 0)) == capi.ERR_INVALID      # ldo < R
+    assert L.bsi_b200_dot_i8(*args(256, 4, 3)) == capi.ERR_INVALID      # BMMA engine needs slice words
+    assert L.bsi_b200_dot_i8(*args(256, 4, 1032)) == capi.ERR_INVALID   # tile width not 64/128/256
