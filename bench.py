@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the BSI tensor-dot hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload fc1|fc2] [--impl reference]
+
+One step = one pass of the hot path over one batch: the fixed76 chunk-scale BSI dot of the named
+workload (FC1-like: Q=512 fp16 activations x R=8192 keys x D=2048; FC2-like: Q=512 x R=2048 x D=8192),
+keys prebuilt, queries packed. ``value`` is effective TOPS = 2*Q*R*D / time with every operand resident
+in HBM; ``e2e`` is the same metric through the public ``bsi_ops`` entry points starting from pinned
+HOST activations and ending with the float32 result back on the host.
+
+N > 1 (launched under torchrun, one rank per GPU): the keys are sharded along R, every rank owns an
+R-row shard of the same size (weak scaling) and there is no data-path collective in the dot itself;
+timing is the max over ranks.
+
+``--impl reference`` times the reference's CPU path (the bsiCPP-semantics port under oracle/) on the
+host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "fc1": dict(Q=512, R=8192, D=2048, name="FC1-like BSI dot Q=512 R=8192 D=2048 (fp16 acts, 1% outliers x20), dp=2, fixed76 chunkscale"),
+    "fc2": dict(Q=512, R=2048, D=8192, name="FC2-like BSI dot Q=512 R=2048 D=8192 (fp16 relu acts), dp=2, fixed76 chunkscale"),
+}
+L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one dot launch, from the ncu capture summarised
+# under profiles/ (None until a capture of that workload exists).
+NCU_TRAFFIC_BYTES = {"fc1": None, "fc2": None}
+
+
+def make_inputs(wl, seed=123):
+    """Seeded synthetic activations/weights with the configuration's shapes and distributions."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    Q, R, D = wl["Q"], wl["R"], wl["D"]
+    q = torch.randn(Q, D, generator=g, dtype=torch.float32)
+    if wl is WORKLOADS["fc1"]:
+        mask = torch.rand(Q, D, generator=g) < 0.01
+        q = torch.where(mask, q * 20.0, q)
+    else:
+        q = torch.relu(q)
+    q = q.to(torch.float16)
+    k = torch.randn(R, D, generator=g, dtype=torch.float32) * 0.02
+    return q, k
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d.get("hbm_gbs"), bf16=d.get("bf16_tflops"), source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run (read-only)."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self.nv is not None and self._thread is None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def cpu_port_rate(q, k, target_s, threads=0):
+    """Times the CPU port on a bounded sample of query rows; returns (TOPS, rows, seconds, threads)."""
+    from oracle import oracle as o
+    keys = o.CpuKeyset(k.numpy(), 2)
+    qn = q.float().numpy()
+    nthreads = o.num_threads() if threads <= 0 else threads
+    rows = min(2 * nthreads, qn.shape[0])
+    t0 = time.perf_counter()
+    keys.dot(qn[:rows], threads)
+    t = time.perf_counter() - t0
+    want = int(max(rows, min(qn.shape[0], rows * target_s / max(t, 1e-6))))
+    want = max(nthreads, (want // nthreads) * nthreads) if want >= nthreads else want
+    want = min(want, qn.shape[0])
+    t0 = time.perf_counter()
+    keys.dot(qn[:want], threads)
+    t = time.perf_counter() - t0
+    ops = 2.0 * want * k.shape[0] * k.shape[1]
+    return ops / t / 1e12, want, t, nthreads
+
+
+def run_reference(args, wl, rank, world):
+    """The reference's CPU implementation of the path (port; the bsiCPP sources are not vendored)."""
+    if rank != 0:
+        return
+    from oracle import oracle as o
+    q, k = make_inputs(wl)
+    keys = o.CpuKeyset(k.numpy(), 2)
+    qn = q.float().numpy()
+    nthreads = o.num_threads()
+    per_step = max(0.2, min(5.0, 150.0 / max(1, args.steps + args.warmup)))
+    rows = min(nthreads, qn.shape[0])
+    t0 = time.perf_counter()
+    keys.dot(qn[:rows])
+    t = time.perf_counter() - t0
+    rows = int(min(qn.shape[0], max(nthreads, rows * per_step / max(t, 1e-6))))
+    for _ in range(args.warmup):
+        keys.dot(qn[:rows])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        keys.dot(qn[:rows])
+    t = time.perf_counter() - t0
+    ops = 2.0 * rows * wl["R"] * wl["D"] * args.steps
+    tops = ops / t / 1e12
+    sample = f"{rows} of {wl['Q']} query rows x all {wl['R']} keys per step"
+    line = {
+        "impl": "reference", "metric": "BSI dot effective TOPS", "value": tops, "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": {"workload": wl["name"], "sample": sample},
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=40)
+    ap.add_argument("--workload", default="fc1", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=30)
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--engine", default="tcgen05")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, wl, rank, world)
+        return
+
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+
+    import bsipytorch_b200
+    from bsipytorch_b200 import capi
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: the BSI path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    ops = bsipytorch_b200.bsi_ops
+    L = capi.lib()
+    Q, R, D = wl["Q"], wl["R"], wl["D"]
+    chunks = D // 256
+    warmup = max(3, args.warmup)
+
+    # Every rank holds its own R-row key shard (weak scaling); shards differ by seed.
+    q, k = make_inputs(wl, seed=123 + rank)
+    q_dev = q.to(dev)
+    keys_cap, *_ = ops.build_bsi_keys_cuda(k.to(dev), 2, 0.5)
+    kt = ops.debug_keys_tensors(keys_cap)
+    qcap = ops.build_bsi_queries_cuda_batch_packed(q_dev, 2, 0.5)
+    qt = ops.debug_query_batch_tensors(qcap)
+
+    # Rotating operand sets so that consecutive steps do not find their operands in L2.
+    set_bytes = kt["q8"].numel() + qt["q8"].numel() + Q * R * 4
+    nsets = max(2, int(-(-2 * L2_BYTES // set_bytes)))
+    sets = []
+    for i in range(nsets):
+        sets.append(dict(a8=qt["q8"].clone(), qs=qt["scales"].clone(), k8=kt["q8"].clone(),
+                         bw0=kt["scales"].clone(), out=torch.empty(Q, R, dtype=torch.float32, device=dev)))
+    engine = {"tcgen05": capi.ENGINE_TCGEN05, "simt": capi.ENGINE_SIMT}.get(args.engine)
+    if engine is None and args.engine.startswith("tcgen05:"):
+        engine = 1000 + int(args.engine.split(":")[1])
+    scale_inv = C.c_float(float(1.0 / 10.0 ** 4))
+
+    def step(i):
+        s = sets[i % nsets]
+        rc = L.bsi_b200_dot_i8(capi.ptr(s["a8"]), s["a8"].shape[1], capi.ptr(s["qs"]), chunks, capi.ptr(s["k8"]),
+                               s["k8"].shape[1], capi.ptr(s["bw0"]), Q, R, chunks, scale_inv, capi.ptr(s["out"]),
+                               R, None, engine, capi.stream_ptr())
+        if rc != 0:
+            capi.check(rc, "bsi_b200_dot_i8")
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    assert torch.equal(sets[0]["out"], sets[1 % nsets]["out"])
+    want_out, *_ = ops.batch_dot_product_multiquery_cuda_batch_caps(qcap, keys_cap)
+    assert torch.equal(sets[0]["out"], want_out), "bench operands give a different result than the bsi_ops path"
+
+    # One CUDA graph of nsets steps; K steps = K // nsets replays + (K % nsets) direct launches.
+    side = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        step(0)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(nsets):
+                step(i)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    K = args.steps
+    reps, rem = divmod(K, nsets)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    ev0.record()
+    for _ in range(reps):
+        graph.replay()
+    for i in range(rem):
+        step(i)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    launches = K
+
+    # End to end through the public entry points, host buffers in and out.
+    x_host = q.pin_memory()
+    out_host = torch.empty(Q, R, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        x = x_host.to(dev, non_blocking=True)
+        cap = ops.build_bsi_queries_cuda_batch_packed(x, 2, 0.5)
+        out, *_ = ops.batch_dot_product_multiquery_cuda_batch_caps(cap, keys_cap)
+        out_host.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    sampler.stop()
+    e2e_ms = e0.elapsed_time(e1)
+    assert torch.equal(out_host, want_out.cpu())
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = float(t[0]), float(t[1])
+    status = ops.device_status()
+
+    if rank == 0:
+        ops_step = 2.0 * Q * R * D * world
+        tops = ops_step * K / (ms * 1e-3) / 1e12
+        e2e_tops = ops_step * args.e2e_steps / (e2e_ms * 1e-3) / 1e12
+        peaks = measured_peaks()
+        int8_peak = 2.0 * peaks["bf16"]
+        per_gpu_tops = tops / world
+        alg_bytes = Q * 7 * D // 8 + R * 6 * D // 8 + Q * chunks * 4 + R * 4 + Q * R * 4
+        line = {
+            "metric": "BSI dot effective TOPS", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": K,
+            "warmup": warmup, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int8 -> int32 (bit-exact with the sliced popcount), fp32 chunk combine",
+            "data": "synthetic",
+            "config": {"workload": wl["name"], "engine": args.engine, "keys_per_gpu": R,
+                       "l2": f"{nsets} rotating operand sets, {nsets * set_bytes / 2**20:.0f} MiB > 126 MiB L2",
+                       "launch": f"CUDA graph of {nsets} steps replayed"},
+            "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": Q * D * 2,
+                    "d2h_bytes_per_step": Q * R * 4, "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps,
+                    "path": "pinned host fp16 -> H2D -> build_bsi_queries_cuda_batch_packed -> batch_dot_product_multiquery_cuda_batch_caps -> D2H fp32"},
+            "gpu_launches": launches,
+            "clocks": sampler.summary(),
+            "roofline": {"bound": "tensor", "achieved": per_gpu_tops, "peak": int8_peak, "unit": "TFLOP/s",
+                         "frac": per_gpu_tops / int8_peak,
+                         "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16']} (dense int8 = 2 x bf16 on this part)",
+                         "traffic": NCU_TRAFFIC_BYTES[args.workload], "kernel": "dot_i8_tcgen05_kernel",
+                         "algorithmic_ops_per_launch": 2.0 * Q * R * D, "algorithmic_bytes_per_launch": alg_bytes,
+                         "hbm_frac_of_measured": (alg_bytes / (ms / K * 1e-3) / 1e9) / peaks["hbm_gbs"]},
+            "device_status": status,
+        }
+        if world == 1:
+            cpu_tops, rows, secs, cores = cpu_port_rate(q, k, args.cpu_seconds)
+            line["cpu_baseline"] = {"value": cpu_tops, "unit": "TOPS", "cores": cores, "kind": "port",
+                                    "sample": f"{rows} of {Q} query rows x all {R} keys, {secs:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
