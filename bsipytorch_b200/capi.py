@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(_PKG, "libbsi_b200.so")
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_TIMEOUT = 0, 1, 2, 3, 4, 5
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 ENGINE_AUTO, ENGINE_TCGEN05, ENGINE_SIMT, ENGINE_BMMA = 0, 1, 2, 3
+EWAH_STATIC_MAX_SLICES = 65536
 
 _vp, _i64, _i32, _f32, _f64 = C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_double
 
@@ -34,6 +35,7 @@ SIGNATURES = {
     "bsi_b200_ewah_decode": (_i32, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "bsi_b200_ewah_scratch_bytes": (_i64, [_i64]),
     "bsi_b200_ewah_encode": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _vp, _vp]),
+    "bsi_b200_ewah_encode_static": (_i32, [_vp, _i64, _i64, _f64, _vp, _i64, _vp, _vp, _vp, _vp, _vp]),
     "bsi_b200_cast_bias": (_i32, [_vp, _i64, _vp, _i64, _i64, _vp, _i64, _i32, _vp]),
 }
 

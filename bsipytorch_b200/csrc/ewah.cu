@@ -358,3 +358,75 @@ extern "C" int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W,
         static_cast<u64>(capacity), reinterpret_cast<u64*>(out), out_len);
     return check_launch("ewah_encode emit launch");
 }
+
+// ---- allocation-free variant ----------------------------------------------------------------------
+// Same pipeline as bsi_b200_ewah_encode, for hosts that have no way to hand us scratch memory:
+// a plugin living inside a process whose own memory manager has already claimed the device, a
+// language binding (cgo, JNI, ctypes) that only owns its input and output buffers, or a serving
+// loop that must not call cudaMalloc/cudaFree because those serialise the whole device. The
+// per-slice popcounts and stream sizes, which the regular entry point keeps in caller-provided
+// scratch, live in one fixed array inside the library image instead. Every GPU that loads the
+// library carries this array until the process exits, which is why it is kept small: room for
+// BSI_B200_EWAH_STATIC_MAX_SLICES slices (2 x 8 bytes each = 1 MiB).
+static __device__ __align__(256) unsigned long long g_ewah_static_scratch[2 * BSI_B200_EWAH_STATIC_MAX_SLICES];
+
+namespace bsi {
+namespace {
+
+// On the host the array's name is only a handle for the runtime, not a device address; the address
+// that kernels may dereference is looked up once per device, with that device current.
+int static_scratch_address(u64** out) {
+    static u64* cached[64] = {nullptr};
+    int dev = 0;
+    BSI_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) {
+        void* p = nullptr;
+        BSI_CUDA_TRY(cudaGetSymbolAddress(&p, g_ewah_static_scratch));
+        *out = static_cast<u64*>(p);
+        return BSI_OK;
+    }
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        BSI_CUDA_TRY(cudaGetSymbolAddress(&p, g_ewah_static_scratch));
+        if (p == nullptr) return fail(BSI_ERR_CUDA, "ewah_encode_static: cudaGetSymbolAddress returned null");
+        cached[dev] = static_cast<u64*>(p);
+    }
+    *out = cached[dev];
+    return BSI_OK;
+}
+
+}  // namespace
+}  // namespace bsi
+
+extern "C" int bsi_b200_ewah_encode_static(const uint64_t* words, int64_t S, int64_t W, double threshold,
+                                           uint64_t* out, int64_t capacity, uint64_t* off, int32_t* out_len,
+                                           int32_t* flags, uint64_t* total, bsi_stream_t stream_) {
+    using namespace bsi;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (S > BSI_B200_EWAH_STATIC_MAX_SLICES) {
+        set_error("ewah_encode_static: S = %lld exceeds the built-in scratch of %d slices; "
+                  "use bsi_b200_ewah_encode with caller-provided scratch",
+                  static_cast<long long>(S), BSI_B200_EWAH_STATIC_MAX_SLICES);
+        return BSI_ERR_UNSUPPORTED;
+    }
+    if (int rc = check_sw("ewah_encode_static", words, S, W)) return rc;
+    if (S == 0) return BSI_OK;
+    if (out == nullptr || off == nullptr || out_len == nullptr || flags == nullptr || capacity < 0)
+        return fail(BSI_ERR_INVALID, "ewah_encode_static: null pointer");
+    u64* scratch = nullptr;
+    if (int rc = static_scratch_address(&scratch)) return rc;
+    // Nothing in the scratch has to start at zero: the first kernel writes counts[s] and sizes[s]
+    // for every s < S before anything reads them, so leftovers of an earlier call are never seen.
+    u64* counts = scratch;
+    u64* sizes = scratch + BSI_B200_EWAH_STATIC_MAX_SLICES;
+    ewah_flags_kernel<true><<<warp_blocks(S), kWarpsPerBlock * 32, 0, stream>>>(
+        reinterpret_cast<const u64*>(words), S, W, threshold, counts, flags, sizes);
+    if (int rc = check_launch("ewah_encode_static flags launch")) return rc;
+    ewah_offsets_kernel<<<1, 1024, 0, stream>>>(sizes, S, reinterpret_cast<u64*>(off),
+                                               reinterpret_cast<u64*>(total));
+    if (int rc = check_launch("ewah_encode_static offsets launch")) return rc;
+    ewah_emit_kernel<<<warp_blocks(S), kWarpsPerBlock * 32, 0, stream>>>(
+        reinterpret_cast<const u64*>(words), S, W, flags, reinterpret_cast<const u64*>(off), sizes,
+        static_cast<u64>(capacity), reinterpret_cast<u64*>(out), out_len);
+    return check_launch("ewah_encode_static emit launch");
+}

@@ -151,6 +151,25 @@ int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W, double thr
                          uint64_t* out, int64_t capacity, uint64_t* off, int32_t* out_len,
                          int32_t* flags, uint64_t* total, bsi_stream_t stream);
 
+/* The same encoder for callers that cannot give the library any scratch memory and cannot let it
+ * allocate: code hosted inside a process whose memory manager already owns the device, bindings
+ * that hold nothing but their inputs and outputs, loops where a cudaMalloc/cudaFree (which
+ * serialise the device) is not acceptable. It has no counterpart in the reference, whose builder
+ * allocates its temporaries through torch on every call (bsi_vector_cuda.cpp:900-941).
+ *
+ * The popcounts and sizes live in an array compiled into the library: BSI_B200_EWAH_STATIC_MAX_SLICES
+ * slices at most, 1 MiB held on every GPU that loads the library until the process exits. A larger S
+ * is refused with BSI_ERR_UNSUPPORTED. The function calls no cudaMalloc, cudaFree or other allocating
+ * routine. Its first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before any stream capture
+ * begins. All calls share the one array, so two calls whose kernels may overlap on the GPU (different
+ * streams, or different host threads) race on it: order them on one stream or with events. Inputs and
+ * outputs are the caller's, exactly as for bsi_b200_ewah_encode. */
+#define BSI_B200_EWAH_STATIC_MAX_SLICES 65536
+int bsi_b200_ewah_encode_static(const uint64_t* words, int64_t S, int64_t W, double threshold,
+                                uint64_t* out, int64_t capacity, uint64_t* off, int32_t* out_len,
+                                int32_t* flags, uint64_t* total, bsi_stream_t stream);
+
 /* ---- layer epilogue ------------------------------------------------------------------
  * y[q][r] = cast(out[q][r]) + cast(bias[r]) in y_dtype (BSI_DTYPE_*), one pass.
  * Replaces the two torch elementwise kernels of BSIQuantizedLinear.forward
