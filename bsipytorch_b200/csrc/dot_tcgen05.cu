@@ -82,17 +82,36 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it reports "not yet":
+// a parked thread issues nothing, so waiting warps do not steal issue slots from the MMA issuer.
+__device__ __forceinline__ bool mbar_try_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Bounded wait. Returns false when the CTA is aborting (this wait or another one timed out).
+// The abort flag and the clock are looked at only every 16th unsuccessful (parked) try.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int site) {
     if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitCycles) {
-            *abort_flag = 1;
-            atomicCAS(&g_device_status, 0, site);
-            return false;
+    long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_parked(bar, parity, 20000u)) return true;
+        if ((spins & 15u) == 0u) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWaitCycles) {
+                *abort_flag = 1;
+                atomicCAS(&g_device_status, 0, site);
+                return false;
+            }
         }
     }
 }
@@ -349,6 +368,8 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_kernel(
     }
 }
 
+#include "dot_tcgen05_pair.cuh"
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -405,6 +426,65 @@ int launch_tile(const CUtensorMap& ma, const CUtensorMap& mb, const float* qs, i
     return check_launch("dot_i8 tcgen05 launch");
 }
 
+template <int BN, bool DBG>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
+                const float* qs, int64_t qs_stride, const float* bw0, int Q, int R, int chunks, float scale_inv,
+                float* out, int64_t ldo, int32_t* dbg, cudaStream_t stream) {
+    using C = pair::Cfg<BN>;
+    static int max_clusters[64] = {0};
+    int dev = 0;
+    BSI_CUDA_TRY(cudaGetDevice(&dev));
+    const int tiles_m = (Q + 255) / 256;
+    const int tiles_n = (R + BN - 1) / BN;
+    const int tiles_total = tiles_m * tiles_n;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(pair::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int resident = 0;
+    if (dev >= 0 && dev < 64) resident = max_clusters[dev];
+    if (resident == 0) {
+        BSI_CUDA_TRY(cudaFuncSetAttribute(pair::dot_i8_tcgen05_pair_kernel<BN, DBG>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
+        BSI_CUDA_TRY(cudaOccupancyMaxActiveClusters(&resident, pair::dot_i8_tcgen05_pair_kernel<BN, DBG>, &cfg));
+        if (resident <= 0) return fail(BSI_ERR_CUDA, "dot_i8: no cluster of 2 CTAs fits on this device");
+        if (dev >= 0 && dev < 64) max_clusters[dev] = resident;
+    }
+    const int pairs = tiles_total < resident ? tiles_total : resident;
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG>, ma, mb, vector_store, qs,
+                                    qs_stride, bw0, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg));
+    return check_launch("dot_i8 tcgen05 pair launch");
+}
+
+// Pair kernel tile width: widest tile unless a narrower one fills more of the machine.
+int pick_bn_pair(int64_t Q, int64_t R) {
+    const int pairs = sm_count() / 2;
+    const int64_t mt = (Q + 255) / 256;
+    const int cand[3] = {256, 128, 64};
+    const double eff[3] = {1.0, 0.85, 0.6};
+    int best = 256;
+    double best_cost = 1e300;
+    for (int i = 0; i < 3; ++i) {
+        const int64_t tiles = mt * ((R + cand[i] - 1) / cand[i]);
+        const int64_t waves = (tiles + pairs - 1) / pairs;
+        const double cost = static_cast<double>(waves) * cand[i] / eff[i];
+        if (cost < best_cost * 0.999) {
+            best_cost = cost;
+            best = cand[i];
+        }
+    }
+    return best;
+}
+
 // Picks the key-tile width: the widest tile wins unless a narrower one fills more SMs.
 int pick_bn(int64_t Q, int64_t R) {
     const int sms = sm_count();
@@ -432,6 +512,30 @@ int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_st
                    float* out, int64_t ldo, int32_t* dbg_iacc, int force_bn, cudaStream_t stream) {
     if (Q > 0x7fffff00ll || R > 0x7fffff00ll || chunks > 0x400000)
         return fail(BSI_ERR_UNSUPPORTED, "dot_i8: Q, R or chunks too large");
+    // force_bn: 0 = automatic; 64/128/256 = single-CTA tiles; 2064/2128/2256 = paired-CTA tiles.
+    const bool want_pair = force_bn ? (force_bn >= 2000) : (Q > 128);
+    if (want_pair) {
+        const int bn = force_bn ? force_bn - 2000 : pick_bn_pair(Q, R);
+        if (bn != 64 && bn != 128 && bn != 256) return fail(BSI_ERR_INVALID, "dot_i8: tile width must be 64, 128 or 256");
+        CUtensorMap ma, mb;
+        if (int rc = make_map(&ma, a8, Q, chunks * 256, lda, BM)) return rc;
+        if (int rc = make_map(&mb, k8, R, chunks * 256, ldk, bn / 2)) return rc;
+        // 16-byte stores need an aligned base, rows a multiple of 4 floats apart and R % 4 == 0
+        const int vector_store =
+            ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo & 3) == 0 && (R & 3) == 0) ? 1 : 0;
+        const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
+#define BSI_PAIR(BN_)                                                                                           \
+    (dbg_iacc ? launch_pair<BN_, true>(ma, mb, vector_store, qs, qs_stride, bw0, q, r, c, scale_inv, out, ldo,  \
+                                       dbg_iacc, stream)                                                         \
+              : launch_pair<BN_, false>(ma, mb, vector_store, qs, qs_stride, bw0, q, r, c, scale_inv, out, ldo, \
+                                        nullptr, stream))
+        switch (bn) {
+            case 256: return BSI_PAIR(256);
+            case 128: return BSI_PAIR(128);
+            default: return BSI_PAIR(64);
+        }
+#undef BSI_PAIR
+    }
     const int bn = force_bn ? force_bn : pick_bn(Q, R);
     CUtensorMap ma, mb;
     if (int rc = make_map(&ma, a8, Q, chunks * 256, lda, BM)) return rc;

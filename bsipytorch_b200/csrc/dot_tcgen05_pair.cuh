@@ -1,0 +1,427 @@
+// Paired-CTA, persistent variant of the int8 tcgen05 dot engine. Included by dot_tcgen05.cu (same
+// translation unit: it shares the PTX wrappers and the device status word).
+//
+// Why pairs: with one CTA per 128 x 256 tile every SM has to pull 48 KB of operands through L2 for
+// every 512 cycles of MMA work (96 B/clk/SM), and the L2->SM fabric delivers about half of that.
+// Two CTAs of a cluster work on one 256 x BN tile with tcgen05.mma.cta_group::2: each CTA loads its
+// own 128 query rows (A) and only HALF of the key rows (B); the pair's tensor cores read B from
+// both shared memories. Operand traffic per SM drops to 32 KB per k-block (64 B/clk/SM at full rate).
+//
+// Why persistent: a pair walks over tiles t = pair, pair + P, ... . Barrier/TMEM set-up happens once,
+// the TMA producer runs ahead into the next tile while the epilogue of the current one drains, and
+// the fp32 result leaves through shared memory as coalesced stores that overlap the next tile's MMAs.
+//
+// Roles per CTA (12 warps; register budget moved with setmaxnreg):
+//   warp 0        TMA producer (both CTAs; every load signals the LEADER's full barrier)
+//   warp 1        MMA issuer (leader CTA only), TMEM alloc/dealloc (both CTAs)
+//   warps 2, 3    idle (they complete the first warpgroup, which gives its registers away)
+//   warps 4..11   epilogue: TMEM -> registers, acc = fmaf(float(I), qs[q][c], acc) per chunk in order;
+//                 at the end of a tile: scale, transpose through smem, coalesced st.global.v4
+//
+// Barriers (same smem offsets in both CTAs):
+//   full[s]    leader's copy used: 1 arrival (leader producer, expect_tx of BOTH CTAs' bytes)
+//   empty[s]   local in each CTA: tcgen05.commit (multicast to both CTAs) after the stage's MMAs
+//   tfull[b]   local in each CTA: multicast commit after a chunk's 8 MMAs
+//   tempty[b]  leader's copy used: one arrival per epilogue warp of BOTH CTAs (16)
+// The accumulator ring holds 512 / BN buffers (2, 4 or 8): with narrow tiles the MMA issuer runs
+// several chunks ahead of the epilogue, which takes the barrier round trip off the critical path.
+// All waits are bounded; a timeout raises the abort flag of both CTAs and every role drains out.
+#pragma once
+
+namespace pair {
+
+constexpr int kThreads = 384;
+constexpr int kEpiWarps = 8;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kRegsLow = 40;
+constexpr int kRegsHigh = 232;
+constexpr long long kWait = 500000000ll;  // ~0.25 s; real waits are microseconds
+
+template <int BN>
+struct Cfg {
+    static constexpr int kHalfN = BN / 2;                 // key rows each CTA loads
+    static constexpr int kABytes = BM * BK;               // 16 KB
+    static constexpr int kBBytes = kHalfN * BK;           // 16 / 8 / 4 KB
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStoreBytes = kEpiWarps * 4096;  // one 32x32 fp32 block per epilogue warp
+    static constexpr int kStages = (BN == 256) ? 6 : (BN == 128 ? 8 : 9);
+    static constexpr int kTmemCols = 512;                 // all of TMEM: 1 CTA per SM anyway
+    static constexpr int kAccBufs = 512 / BN;             // accumulator ring: 2, 4 or 8 buffers of BN columns
+    static constexpr int kBarriers = 2 * kStages + 2 * kAccBufs + 1;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarriers * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    // Plain (CTA-scope release) arrive: the ordering that matters here -- TMEM reads done before the
+    // accumulator is overwritten -- comes from tcgen05.wait::ld + tcgen05.fence::before_thread_sync.
+    // A cluster-scope release would put a full memory barrier into every chunk of the epilogue.
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void store_flag_cluster(uint32_t cluster_addr, int v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on the barrier at this smem offset in BOTH CTAs of the pair once all earlier MMAs are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(mask)
+        : "memory");
+}
+
+// M = 256 across the pair.
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+           (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+struct AbortCtx {
+    volatile int* flag;    // this CTA's abort flag
+    uint32_t peer_flag;    // cluster address of the peer's
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, const AbortCtx& a, int site) {
+    if (mbar_try(bar, parity)) return true;
+    long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        if (mbar_try_parked(bar, parity, 20000u)) return true;
+        if ((spins & 15u) == 0u) {
+            if (*a.flag) return false;
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > kWait) {
+                *a.flag = 1;
+                store_flag_cluster(a.peer_flag, 1);
+                atomicCAS(&g_device_status, 0, 16 + site);
+                return false;
+            }
+        }
+    }
+}
+
+template <int BN, bool DBG>
+__global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
+    const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+    int vector_store,
+    const float* __restrict__ qs, int64_t qs_stride, const float* __restrict__ bw0,
+    int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
+    float* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc) {
+    using C = Cfg<BN>;
+    constexpr int kStages = C::kStages;
+    constexpr int kCols = BN / 2;       // accumulator columns per epilogue warp
+    constexpr int kGroups = kCols / 32; // tcgen05.ld / store rounds per warp
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* store_area = smem + kStages * C::kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(store_area + C::kStoreBytes);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kBarriers);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t bar_base = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    constexpr int kAccBufs = C::kAccBufs;
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + kAccBufs + b); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 2 * kAccBufs);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair_id = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+    const int num_kb = chunks * 2;
+
+    AbortCtx actx;
+    actx.flag = abort_flag;
+    actx.peer_flag = map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u);
+
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < kAccBufs; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 2 * kEpiWarps);
+        }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    // Cluster barrier split around the TMEM allocation: arrive now (thread 0's barrier inits are
+    // released by its own arrive), wait after the allocation, so the two latencies overlap.
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(C::kTmemCols)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    // both CTAs' barriers are initialised before anyone touches the peer's
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < kFirstEpiWarp) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));
+        if (warp == 0 && lane == 0) {
+            // ---------------- TMA producer ----------------
+            int issued = 0, it = 0;
+            bool ok = true;
+            for (int tile = pair_id; tile < tiles_total && ok; tile += num_pairs) {
+                const int tm = tile % tiles_m;
+                const int tn = tile / tiles_m;
+                const int row_a = tm * 256 + static_cast<int>(rank) * BM;
+                const int row_b = tn * BN + static_cast<int>(rank) * C::kHalfN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = static_cast<uint32_t>(it / kStages) & 1u;
+                    if (!wait_or_abort(empty_bar(s), ph ^ 1u, actx, 1)) { ok = false; break; }
+                    const uint32_t leader_full = map_to_cta(full_bar(s), 0);
+                    if (leader) mbar_expect_tx(full_bar(s), 2u * C::kStageBytes);
+                    const uint32_t a_dst = smem_base + s * C::kStageBytes;
+                    tma_load_2d_pair(a_dst, &map_a, kb * BK, row_a, leader_full);
+                    tma_load_2d_pair(a_dst + C::kABytes, &map_b, kb * BK, row_b, leader_full);
+                    issued = it + 1;
+                }
+            }
+            if (*abort_flag && leader) {
+                // Let the copies that were issued land before the pair gives its smem back.
+                const int first = issued > kStages ? issued - kStages : 0;
+                for (int k = first; k < issued; ++k) {
+                    const long long t0 = clock64();
+                    while (!mbar_try(full_bar(k % kStages), static_cast<uint32_t>(k / kStages) & 1u) &&
+                           clock64() - t0 < kWait / 64) {}
+                }
+            }
+        } else if (warp == 1 && leader) {
+            // ---------------- MMA issuer (leader CTA) ----------------
+            // The whole warp walks the loop (so that addresses and descriptors stay in the uniform
+            // datapath) and one elected lane issues the tensor-core instructions.
+            constexpr uint32_t idesc = umma_idesc_pair(BN);
+            int it = 0, cc = 0;
+            bool ok = true;
+            for (int tile = pair_id; tile < tiles_total && ok; tile += num_pairs) {
+                for (int c = 0; c < chunks && ok; ++c, ++cc) {
+                    const int b = cc % kAccBufs;
+                    const uint32_t tph = static_cast<uint32_t>(cc / kAccBufs) & 1u;
+                    if (!wait_or_abort(tempty_bar(b), tph ^ 1u, actx, 3)) { ok = false; break; }
+                    const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(b * BN);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half, ++it) {
+                        const int s = it % kStages;
+                        const uint32_t ph = static_cast<uint32_t>(it / kStages) & 1u;
+                        if (!wait_or_abort(full_bar(s), ph, actx, 2)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_addr = smem_base + s * C::kStageBytes;
+                        const uint64_t adesc = umma_desc(a_addr);
+                        const uint64_t bdesc = umma_desc(a_addr + C::kABytes);
+                        if (elect_one()) {
+#pragma unroll
+                            for (int k = 0; k < BK / UMMA_K; ++k) {
+                                umma_i8_pair(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc,
+                                             (half | k) != 0 ? 1u : 0u);
+                            }
+                            umma_commit_pair(empty_bar(s));
+                            if (half == 1) umma_commit_pair(tfull_bar(b));
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+            if (!ok && lane == 0) {
+                umma_commit(drain_bar);
+                const long long t0 = clock64();
+                while (!mbar_try(drain_bar, 0) && clock64() - t0 < kWait / 64) {}
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsHigh));
+        // ---------------- epilogue ----------------
+        const int ew = warp - kFirstEpiWarp;   // 0..7
+        const int quad = warp & 3;             // TMEM lane quadrant this warp may read
+        const int half = ew >> 2;              // which half of the BN columns
+        const int col0 = half * kCols;
+        uint8_t* my_store = store_area + ew * 4096;
+        const uint32_t leader_tempty0 = map_to_cta(tempty_bar(0), 0);
+
+        float acc[kCols];
+        int cc = 0;
+        bool ok = true;
+        for (int tile = pair_id; tile < tiles_total && ok; tile += num_pairs) {
+            const int tm = tile % tiles_m;
+            const int tn = tile / tiles_m;
+            const int row = tm * 256 + static_cast<int>(rank) * BM + quad * 32 + lane;
+            const int n0 = tn * BN;
+            const bool row_ok = row < Q;
+            const float* qs_row = qs + static_cast<int64_t>(row_ok ? row : 0) * (qs_stride ? qs_stride : 1);
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) acc[j] = 0.0f;
+            // Key scales of this warp's columns: lane L keeps columns 4L..4L+3 (of the warp's kCols) in
+            // registers; the load's latency hides behind the mainloop and the store phase fetches them
+            // with shuffles.
+            float bwreg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (lane * 4 < kCols) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = n0 + col0 + lane * 4 + e;
+                    if (col < R) bwreg[e] = __ldg(bw0 + col);
+                }
+            }
+
+            for (int c = 0; c < chunks && ok; ++c, ++cc) {
+                const int b = cc % kAccBufs;
+                const uint32_t tph = static_cast<uint32_t>(cc / kAccBufs) & 1u;
+                const float qscale = qs_stride ? __ldg(qs_row + c) : __ldg(qs_row);
+                if (!wait_or_abort(tfull_bar(b), tph, actx, 4)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                       static_cast<uint32_t>(b * BN + col0);
+                int32_t v[2][32];
+                tmem_ld32(taddr, v[0]);
+#pragma unroll
+                for (int j = 0; j < kGroups; ++j) {
+                    tmem_ld_wait();
+                    if (j + 1 < kGroups) tmem_ld32(taddr + (j + 1) * 32, v[(j + 1) & 1]);
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        acc[j * 32 + e] = __fmaf_rn(static_cast<float>(v[j & 1][e]), qscale, acc[j * 32 + e]);
+                    }
+                    if (DBG) {
+                        if (row_ok) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                const int col = n0 + col0 + j * 32 + e;
+                                if (col < R)
+                                    dbg_iacc[(static_cast<int64_t>(row) * R + col) * chunks + c] = v[j & 1][e];
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8u * b);
+            }
+            if (!ok) break;
+
+            // ---- tile result: out = (acc * bw0[r]) * scale_inv ----
+            // A lane owns a row; 32 x 32 blocks go through this warp's 4 KB of smem (16-byte chunks
+            // XOR-swizzled by row so that both directions are conflict free) and leave as
+            // st.global.v4 with 8 lanes per 128-byte row segment: every store instruction writes
+            // four full 128-byte lines. Plain stores are fire-and-forget, so the warp moves on to
+            // the next tile (or exits) while they drain.
+            const int row_base = tm * 256 + static_cast<int>(rank) * BM + quad * 32;
+            if (vector_store) {
+#pragma unroll
+                for (int g = 0; g < kGroups; ++g) {
+                    const int colg = n0 + col0 + g * 32;
+                    uint8_t* dst = my_store + lane * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        float4 w;
+                        w.x = __shfl_sync(0xffffffffu, bwreg[0], g * 8 + ch);
+                        w.y = __shfl_sync(0xffffffffu, bwreg[1], g * 8 + ch);
+                        w.z = __shfl_sync(0xffffffffu, bwreg[2], g * 8 + ch);
+                        w.w = __shfl_sync(0xffffffffu, bwreg[3], g * 8 + ch);
+                        float4 o;
+                        o.x = (acc[g * 32 + ch * 4 + 0] * w.x) * scale_inv;
+                        o.y = (acc[g * 32 + ch * 4 + 1] * w.y) * scale_inv;
+                        o.z = (acc[g * 32 + ch * 4 + 2] * w.z) * scale_inv;
+                        o.w = (acc[g * 32 + ch * 4 + 3] * w.w) * scale_inv;
+                        *reinterpret_cast<float4*>(dst + ((ch ^ (lane & 7)) << 4)) = o;
+                    }
+                    __syncwarp();
+                    const int cchunk = lane & 7;
+                    const int col = colg + cchunk * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + (lane >> 3);
+                        const float4 o = *reinterpret_cast<const float4*>(my_store + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
+                        const int grow = row_base + rr;
+                        if (grow < Q && col < R) {   // R % 4 == 0 on this path, so col < R covers col + 3
+                            *reinterpret_cast<float4*>(out + static_cast<int64_t>(grow) * ldo + col) = o;
+                        }
+                    }
+                    __syncwarp();
+                }
+            } else {
+                float* orow = out + static_cast<int64_t>(row_ok ? row : 0) * ldo;
+#pragma unroll
+                for (int j = 0; j < kCols; ++j) {
+                    const int col = n0 + col0 + j;
+                    const float w = __shfl_sync(0xffffffffu, bwreg[j & 3], j >> 2);
+                    if (row_ok && col < R) orow[col] = (acc[j] * w) * scale_inv;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    __syncwarp();
+    cluster_sync_all();  // the peer may still be reading this CTA's smem or arriving on its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"(static_cast<uint32_t>(C::kTmemCols)) : "memory");
+    }
+}
+
+}  // namespace pair

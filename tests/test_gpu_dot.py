@@ -14,8 +14,10 @@ from oracle import oracle as o
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
+# 1000 + n pins single-CTA tiles of width n; 3000 + n pins paired-CTA (cta_group::2) tiles of width n
 ENGINES = {"simt": capi.ENGINE_SIMT, "tcgen05": capi.ENGINE_TCGEN05, "tcgen05_bn64": 1064,
-           "tcgen05_bn128": 1128, "tcgen05_bn256": 1256}
+           "tcgen05_bn128": 1128, "tcgen05_bn256": 1256, "pair_bn64": 3064, "pair_bn128": 3128,
+           "pair_bn256": 3256}
 
 
 def _prepare(q, k, bits_q=7, bits_k=6, chunk_mode=True, dp=2):
@@ -38,7 +40,7 @@ def _assert_bits(got, want):
 
 
 SHAPES = [(64, 256, 2048), (70, 100, 512), (200, 300, 1024), (128, 256, 256), (1, 1, 256), (130, 513, 768),
-          (33, 65, 250)]
+          (33, 65, 250), (512, 1100, 512), (300, 2000, 256)]
 
 
 @pytest.mark.parametrize("engine", list(ENGINES))
