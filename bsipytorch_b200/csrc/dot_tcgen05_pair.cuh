@@ -12,9 +12,9 @@
 // the fp32 result leaves through shared memory as coalesced stores that overlap the next tile's MMAs.
 //
 // Roles per CTA (12 warps; register budget moved with setmaxnreg):
-//   warp 0        TMA producer (both CTAs; every load signals the LEADER's full barrier)
+//   warps 0, 2, 3 TMA producers, k-blocks round robin (both CTAs; every load signals the LEADER's
+//                 full barrier)
 //   warp 1        MMA issuer (leader CTA only), TMEM alloc/dealloc (both CTAs)
-//   warps 2, 3    idle (they complete the first warpgroup, which gives its registers away)
 //   warps 4..11   epilogue: TMEM -> registers, acc = fmaf(float(I), qs[q][c], acc) per chunk in order;
 //                 at the end of a tile: scale, transpose through smem, coalesced st.global.v4
 //
@@ -184,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const int num_pairs = gridDim.x >> 1;
     const int num_kb = chunks * 2;
 
+    const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
     AbortCtx actx;
     actx.flag = abort_flag;
     actx.peer_flag = map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u);
@@ -221,9 +222,14 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
 
     if (warp < kFirstEpiWarp) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));
-        if (warp == 0 && lane == 0) {
-            // ---------------- TMA producer ----------------
-            int issued = 0, it = 0;
+        if (warp != 1 && lane == 0) {
+            // ---------------- TMA producers ----------------
+            // One thread needs ~450 cycles per k-block (empty wait, expect_tx, two tensor copies), which
+            // is slower than the MMAs consume narrow tiles; warps 0, 2 and 3 therefore take the k-blocks
+            // round robin. Stage s = it % kStages is always filled by the producer that owns `it`.
+            constexpr int kProducers = 3;
+            const int me = warp == 0 ? 0 : warp - 1;
+            int it = 0;
             bool ok = true;
             for (int tile = pair_id; tile < tiles_total && ok; tile += num_pairs) {
                 const int tm = tile % tiles_m;
@@ -231,24 +237,14 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 const int row_a = tm * 256 + static_cast<int>(rank) * BM;
                 const int row_b = tn * BN + static_cast<int>(rank) * C::kHalfN;
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    if (it % kProducers != me) continue;
                     const int s = it % kStages;
                     const uint32_t ph = static_cast<uint32_t>(it / kStages) & 1u;
                     if (!wait_or_abort(empty_bar(s), ph ^ 1u, actx, 1)) { ok = false; break; }
-                    const uint32_t leader_full = map_to_cta(full_bar(s), 0);
                     if (leader) mbar_expect_tx(full_bar(s), 2u * C::kStageBytes);
                     const uint32_t a_dst = smem_base + s * C::kStageBytes;
-                    tma_load_2d_pair(a_dst, &map_a, kb * BK, row_a, leader_full);
-                    tma_load_2d_pair(a_dst + C::kABytes, &map_b, kb * BK, row_b, leader_full);
-                    issued = it + 1;
-                }
-            }
-            if (*abort_flag && leader) {
-                // Let the copies that were issued land before the pair gives its smem back.
-                const int first = issued > kStages ? issued - kStages : 0;
-                for (int k = first; k < issued; ++k) {
-                    const long long t0 = clock64();
-                    while (!mbar_try(full_bar(k % kStages), static_cast<uint32_t>(k / kStages) & 1u) &&
-                           clock64() - t0 < kWait / 64) {}
+                    tma_load_2d_pair(a_dst, &map_a, kb * BK, row_a, leader_full0 + 8u * s);
+                    tma_load_2d_pair(a_dst + C::kABytes, &map_b, kb * BK, row_b, leader_full0 + 8u * s);
                 }
             }
         } else if (warp == 1 && leader) {
@@ -413,6 +409,11 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
         }
     }
 
+    if (threadIdx.x == 0 && *abort_flag) {
+        // Error path only: give copies that are still in flight time to land before the smem goes away.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 4000000ll) {}
+    }
     tc_fence_before();
     __syncthreads();
     __syncwarp();

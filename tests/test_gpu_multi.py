@@ -1,0 +1,54 @@
+"""R-sharded BSI linears over NCCL: a sharded model reproduces the single-GPU outputs bit for bit.
+
+Needs at least 2 GPUs (skipped otherwise). Ranks are child processes, one per GPU, rendezvous on
+127.0.0.1; NVLS is switched off so that no rank's memory is bound to a multicast object."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_path):
+    import torch.distributed as dist
+
+    from bsipytorch_b200 import opt
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        cfg = opt.OPTConfig(vocab_size=512, hidden_size=512, num_hidden_layers=2, num_attention_heads=8, ffn_dim=2048,
+                            max_position_embeddings=128, name="tiny")
+        model = opt.build_opt_bsi(cfg, dtype=torch.float16, device=f"cuda:{rank}", seed=11, rank=rank, world=world)
+        ids = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(2)).to(f"cuda:{rank}")
+        with torch.no_grad():
+            logits = model(ids)
+        if rank == 0:
+            single = opt.build_opt_bsi(cfg, dtype=torch.float16, device="cuda:0", seed=11)
+            with torch.no_grad():
+                want = single(ids)
+            torch.save({"equal": bool(torch.equal(logits, want)), "finite": bool(torch.isfinite(logits).all())}, out_path)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_sharded_opt_equals_single_gpu(tmp_path):
+    world = 2
+    out_path = str(tmp_path / "result.pt")
+    mp.spawn(_worker, args=(world, _free_port(), out_path), nprocs=world, join=True)
+    res = torch.load(out_path)
+    assert res["finite"] and res["equal"]
