@@ -74,10 +74,17 @@ int dtype_code(const at::Tensor& t) {
 }
 
 at::Tensor slice_weight_base(int S, const at::Device& dev) {
-    // +-2^i with the top slice negative (bsi_cuda.cpp:217-236, bsi_vector_cuda.cpp:1028).
+    // +-2^i with the top slice negative (bsi_cuda.cpp:217-236, bsi_vector_cuda.cpp:1028); cached per
+    // (S, device) like the reference's make_slice_weights_cuda_cached (bsi_vector_cuda.cpp:69-88).
+    static std::unordered_map<int64_t, at::Tensor> cache;
+    const int64_t key = (static_cast<int64_t>(dev.index()) << 8) | S;
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
     std::vector<float> w(S);
     for (int i = 0; i < S; ++i) w[i] = std::ldexp(1.0f, i) * ((i == S - 1) ? -1.0f : 1.0f);
-    return torch::tensor(w, torch::dtype(torch::kFloat32)).to(dev);
+    at::Tensor t = torch::tensor(w, torch::dtype(torch::kFloat32)).to(dev);
+    cache[key] = t;
+    return t;
 }
 
 // ---- holders behind the capsules (bsi_cuda.cpp:146-215) ------------------------------------------
@@ -123,7 +130,10 @@ T* from_capsule(const py::capsule& cap, const char* name) {
 uint64_t g_last_quantize_ns = 0, g_last_pack_ns = 0, g_last_total_ns = 0;
 
 // Quantise + pack `x` ([rows, d], f32/f16/bf16, CPU or CUDA) in one kernel.
-PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chunk_mode, bool profile) {
+// lean = true skips the bit slices and slice weights (only the int8 image and the scales are
+// produced): what the fused linear path needs.
+PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chunk_mode, bool profile,
+                 bool lean = false) {
     TORCH_CHECK(input.dim() == 2, "expects 2D tensor [rows, d]");
     check_clip();
     const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
@@ -144,12 +154,14 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
     auto opt = [&](at::ScalarType t) { return at::TensorOptions().dtype(t).device(dev); };
     // Partial last words / empty inputs rely on zero-initialised words, as the reference's do.
     const bool ragged = (b.d % 64) != 0 || b.rows == 0 || b.d == 0;
-    b.words = ragged ? at::zeros({b.rows, bits, b.W}, opt(at::kLong)) : at::empty({b.rows, bits, b.W}, opt(at::kLong));
+    if (!lean)
+        b.words = ragged ? at::zeros({b.rows, bits, b.W}, opt(at::kLong)) : at::empty({b.rows, bits, b.W}, opt(at::kLong));
     if (chunk_mode) b.scales = at::ones({b.rows, std::max<int64_t>(b.chunks, 0)}, opt(at::kFloat));
     else b.scales = at::ones({b.rows}, opt(at::kFloat));
     b.q8 = at::empty({b.rows, ld8}, opt(at::kChar));
     if (b.rows == 0 || b.d == 0) {
         b.q8.zero_();
+        if (lean) b.words = at::zeros({b.rows, bits, b.W}, opt(at::kLong));
         b.slice_weights = slice_weight_base(bits, dev).unsqueeze(0).expand({b.rows, bits}).contiguous();
         return b;
     }
@@ -163,7 +175,7 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
     }
     check_status(bsi_b200_quantize_pack(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, bits,
                                         chunk_mode ? 1 : 0,
-                                        reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
+                                        lean ? nullptr : reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
                                         b.scales.data_ptr<float>(), nullptr, b.q8.data_ptr<int8_t>(), ld8,
                                         current_stream()),
                  "bsi_b200_quantize_pack");
@@ -174,6 +186,7 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
     }
+    if (lean) return b;
     auto base = slice_weight_base(bits, dev).unsqueeze(0);
     if (chunk_mode) b.slice_weights = base.expand({b.rows, bits}).contiguous();
     else b.slice_weights = (base * b.scales.unsqueeze(1)).contiguous();  // bsi_vector_cuda.cpp:1042,1157
@@ -182,13 +195,13 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
 
 // Queries get chunk scales when enabled and the word count allows 256-bit chunks
 // (bsi_vector_cuda.cpp:980-994).
-PackedBatch pack_queries(const at::Tensor& q2d, int decimal_places) {
+PackedBatch pack_queries(const at::Tensor& q2d, int decimal_places, bool lean = false) {
     const int bits = bits_queries();
     const int64_t d = q2d.size(1);
     const int W = d > 0 ? static_cast<int>((d + 63) / 64) : 1;
     const bool chunk = chunk_scale_enabled() && (W % 4 == 0);
     const bool profile = profile_enabled() && q2d.is_cuda();
-    PackedBatch b = pack(q2d, decimal_places, bits, chunk, profile);
+    PackedBatch b = pack(q2d, decimal_places, bits, chunk, profile, lean);
     // One fused kernel does quantise and pack; its time is reported as the pack time.
     g_last_quantize_ns = 0;
     g_last_pack_ns = profile ? static_cast<uint64_t>(b.quantize_ms * 1.0e6) : 0;
@@ -482,21 +495,38 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
                               int decimalPlaces) {
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
-    PackedBatch qb = pack_queries(x2d, decimalPlaces);
-    py::tuple r = run_dot(qb, *keys, false, nullptr);
-    at::Tensor out = r[0].cast<at::Tensor>();
-    const int64_t Q = out.size(0), R = out.size(1);
+    const int engine = engine_from_env();
+    const bool fused = engine == BSI_ENGINE_AUTO || engine == BSI_ENGINE_TCGEN05;
+    PackedBatch qb = pack_queries(x2d, decimalPlaces, /*lean=*/fused);
+    const int64_t Q = qb.rows, R = keys->num_keys;
+    TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
+    TORCH_CHECK(qb.W == keys->b.W, "Word count mismatch between query batch and keys");
+    TORCH_CHECK(qb.decimals == keys->b.decimals, "Decimal mismatch between queries and keys: q=", qb.decimals,
+                " k=", keys->b.decimals);
+    const int total_decimals = qb.decimals + keys->b.decimals;
+    const double scale_inv = total_decimals > 0 ? 1.0 / std::pow(10.0, total_decimals) : 1.0;
     at::ScalarType yt = x2d.scalar_type();
     if (!(yt == at::kFloat || yt == at::kHalf || yt == at::kBFloat16)) yt = at::kFloat;
-    at::Tensor y = at::empty({Q, R}, out.options().dtype(yt));
+    at::Tensor y = at::empty({Q, R}, qb.q8.options().dtype(yt));
     const float* bptr = nullptr;
     at::Tensor b32;
     if (bias.has_value() && bias->defined()) {
-        b32 = bias->to(out.device(), at::kFloat).contiguous();
+        b32 = bias->to(y.device(), at::kFloat).contiguous();
         TORCH_CHECK(b32.numel() == R, "bias length mismatch");
         bptr = b32.data_ptr<float>();
     }
     const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
+    if (fused) {
+        check_status(bsi_b200_linear_i8(qb.q8.data_ptr<int8_t>(), qb.q8.size(1), qb.scales.data_ptr<float>(),
+                                        qb.chunk_mode ? qb.chunks : 0, keys->b.q8.data_ptr<int8_t>(),
+                                        keys->b.q8.size(1), keys->b.scales.data_ptr<float>(), bptr, Q, R, qb.chunks,
+                                        static_cast<float>(scale_inv), y.data_ptr(), R, code, current_stream()),
+                     "bsi_b200_linear_i8");
+        return y;
+    }
+    // other engines: float32 dot, then the separate cast + bias kernel
+    py::tuple r = run_dot(qb, *keys, false, nullptr);
+    at::Tensor out = r[0].cast<at::Tensor>();
     check_status(bsi_b200_cast_bias(out.data_ptr<float>(), R, bptr, Q, R, y.data_ptr(), R, code, current_stream()),
                  "bsi_b200_cast_bias");
     return y;

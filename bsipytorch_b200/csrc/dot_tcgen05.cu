@@ -24,6 +24,8 @@
 // word, raises a CTA-wide abort flag, every role leaves its loop, outstanding copies and MMAs
 // are waited for (bounded again), TMEM is freed and the kernel returns.
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
@@ -426,10 +428,10 @@ int launch_tile(const CUtensorMap& ma, const CUtensorMap& mb, const float* qs, i
     return check_launch("dot_i8 tcgen05 launch");
 }
 
-template <int BN, bool DBG>
+template <int BN, bool DBG, typename OutT>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
-                const float* qs, int64_t qs_stride, const float* bw0, int Q, int R, int chunks, float scale_inv,
-                float* out, int64_t ldo, int32_t* dbg, cudaStream_t stream) {
+                const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
+                float scale_inv, void* out, int64_t ldo, int32_t* dbg, cudaStream_t stream) {
     using C = pair::Cfg<BN>;
     static int max_clusters[64] = {0};
     int dev = 0;
@@ -451,17 +453,17 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     int resident = 0;
     if (dev >= 0 && dev < 64) resident = max_clusters[dev];
     if (resident == 0) {
-        BSI_CUDA_TRY(cudaFuncSetAttribute(pair::dot_i8_tcgen05_pair_kernel<BN, DBG>,
+        BSI_CUDA_TRY(cudaFuncSetAttribute(pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
-        BSI_CUDA_TRY(cudaOccupancyMaxActiveClusters(&resident, pair::dot_i8_tcgen05_pair_kernel<BN, DBG>, &cfg));
+        BSI_CUDA_TRY(cudaOccupancyMaxActiveClusters(&resident, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>, &cfg));
         if (resident <= 0) return fail(BSI_ERR_CUDA, "dot_i8: no cluster of 2 CTAs fits on this device");
         if (dev >= 0 && dev < 64) max_clusters[dev] = resident;
     }
     const int pairs = tiles_total < resident ? tiles_total : resident;
     cfg.gridDim = dim3(2 * pairs, 1, 1);
-    BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG>, ma, mb, vector_store, qs,
-                                    qs_stride, bw0, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg));
+    BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>, ma, mb, vector_store, qs,
+                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg));
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
@@ -507,6 +509,43 @@ int pick_bn(int64_t Q, int64_t R) {
 
 }  // namespace
 
+// Paired-CTA engine with the output type and the bias chosen at run time (y_dtype: BSI_DTYPE_*).
+int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride, const int8_t* k8, int64_t ldk,
+                const float* bw0, const float* bias, int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, cudaStream_t stream) {
+    if (Q > 0x7fffff00ll || R > 0x7fffff00ll || chunks > 0x400000)
+        return fail(BSI_ERR_UNSUPPORTED, "dot_i8: Q, R or chunks too large");
+    const int bn = force_bn ? force_bn : pick_bn_pair(Q, R);
+    if (bn != 64 && bn != 128 && bn != 256) return fail(BSI_ERR_INVALID, "dot_i8: tile width must be 64, 128 or 256");
+    if (dbg_iacc != nullptr && y_dtype != BSI_DTYPE_F32)
+        return fail(BSI_ERR_INVALID, "dot_i8: the accumulator dump is only available with float32 output");
+    CUtensorMap ma, mb;
+    if (int rc = make_map(&ma, a8, Q, chunks * 256, lda, BM)) return rc;
+    if (int rc = make_map(&mb, k8, R, chunks * 256, ldk, bn / 2)) return rc;
+    // 16-byte stores need an aligned base, a row pitch that is a multiple of 16 bytes and R a multiple
+    // of the values per 16 bytes; anything else takes the scalar store path
+    const int esz = y_dtype == BSI_DTYPE_F32 ? 4 : 2;
+    const int per16 = 16 / esz;
+    const int vector_store =
+        ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo % per16) == 0 && (R % per16) == 0) ? 1 : 0;
+    const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
+#define BSI_PAIR_T(BN_, DBG_, T_)                                                                              \
+    launch_pair<BN_, DBG_, T_>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv, out, ldo,  \
+                               dbg_iacc, stream)
+#define BSI_PAIR(BN_)                                                                   \
+    (y_dtype == BSI_DTYPE_F16    ? BSI_PAIR_T(BN_, false, __half)                       \
+     : y_dtype == BSI_DTYPE_BF16 ? BSI_PAIR_T(BN_, false, __nv_bfloat16)                \
+     : dbg_iacc                  ? BSI_PAIR_T(BN_, true, float)                         \
+                                 : BSI_PAIR_T(BN_, false, float))
+    switch (bn) {
+        case 256: return BSI_PAIR(256);
+        case 128: return BSI_PAIR(128);
+        default: return BSI_PAIR(64);
+    }
+#undef BSI_PAIR
+#undef BSI_PAIR_T
+}
+
 int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride, const int8_t* k8,
                    int64_t ldk, const float* bw0, int64_t Q, int64_t R, int64_t chunks, float scale_inv,
                    float* out, int64_t ldo, int32_t* dbg_iacc, int force_bn, cudaStream_t stream) {
@@ -515,26 +554,8 @@ int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_st
     // force_bn: 0 = automatic; 64/128/256 = single-CTA tiles; 2064/2128/2256 = paired-CTA tiles.
     const bool want_pair = force_bn ? (force_bn >= 2000) : (Q > 128);
     if (want_pair) {
-        const int bn = force_bn ? force_bn - 2000 : pick_bn_pair(Q, R);
-        if (bn != 64 && bn != 128 && bn != 256) return fail(BSI_ERR_INVALID, "dot_i8: tile width must be 64, 128 or 256");
-        CUtensorMap ma, mb;
-        if (int rc = make_map(&ma, a8, Q, chunks * 256, lda, BM)) return rc;
-        if (int rc = make_map(&mb, k8, R, chunks * 256, ldk, bn / 2)) return rc;
-        // 16-byte stores need an aligned base, rows a multiple of 4 floats apart and R % 4 == 0
-        const int vector_store =
-            ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo & 3) == 0 && (R & 3) == 0) ? 1 : 0;
-        const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
-#define BSI_PAIR(BN_)                                                                                           \
-    (dbg_iacc ? launch_pair<BN_, true>(ma, mb, vector_store, qs, qs_stride, bw0, q, r, c, scale_inv, out, ldo,  \
-                                       dbg_iacc, stream)                                                         \
-              : launch_pair<BN_, false>(ma, mb, vector_store, qs, qs_stride, bw0, q, r, c, scale_inv, out, ldo, \
-                                        nullptr, stream))
-        switch (bn) {
-            case 256: return BSI_PAIR(256);
-            case 128: return BSI_PAIR(128);
-            default: return BSI_PAIR(64);
-        }
-#undef BSI_PAIR
+        return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, nullptr, Q, R, chunks, scale_inv, out, ldo,
+                           BSI_DTYPE_F32, dbg_iacc, force_bn ? force_bn - 2000 : 0, stream);
     }
     const int bn = force_bn ? force_bn : pick_bn(Q, R);
     CUtensorMap ma, mb;

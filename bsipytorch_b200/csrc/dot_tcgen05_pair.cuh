@@ -148,13 +148,33 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, con
     }
 }
 
-template <int BN, bool DBG>
+// Last step of one output element. float: the raw dot value (the microbenchmark entry point).
+// half / bfloat16: the layer epilogue of the reference, `scores.to(dtype) + bias.to(dtype)`
+// (verify_accuracy_bsi.py:193-195): both terms are narrowed first, added, and narrowed again.
+template <typename OutT>
+__device__ __forceinline__ OutT finish(float v, float bias, bool has_bias);
+template <>
+__device__ __forceinline__ float finish<float>(float v, float bias, bool has_bias) {
+    return has_bias ? v + bias : v;
+}
+template <>
+__device__ __forceinline__ __half finish<__half>(float v, float bias, bool has_bias) {
+    const __half h = __float2half_rn(v);
+    return has_bias ? __float2half_rn(__half2float(h) + __half2float(__float2half_rn(bias))) : h;
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 finish<__nv_bfloat16>(float v, float bias, bool has_bias) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    return has_bias ? __float2bfloat16_rn(__bfloat162float(h) + __bfloat162float(__float2bfloat16_rn(bias))) : h;
+}
+
+template <int BN, bool DBG, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
     int vector_store,
     const float* __restrict__ qs, int64_t qs_stride, const float* __restrict__ bw0,
-    int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
-    float* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc) {
+    const float* __restrict__ bias, int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
+    void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     constexpr int kCols = BN / 2;       // accumulator columns per epilogue warp
@@ -183,6 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const int pair_id = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     const int num_kb = chunks * 2;
+    const bool has_bias = bias != nullptr;
 
     const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
     AbortCtx actx;
@@ -314,11 +335,15 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
             // registers; the load's latency hides behind the mainloop and the store phase fetches them
             // with shuffles.
             float bwreg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float biasreg[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             if (lane * 4 < kCols) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int col = n0 + col0 + lane * 4 + e;
-                    if (col < R) bwreg[e] = __ldg(bw0 + col);
+                    if (col < R) {
+                        bwreg[e] = __ldg(bw0 + col);
+                        if (has_bias) biasreg[e] = __ldg(bias + col);
+                    }
                 }
             }
 
@@ -364,46 +389,54 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
             // four full 128-byte lines. Plain stores are fire-and-forget, so the warp moves on to
             // the next tile (or exits) while they drain.
             const int row_base = tm * 256 + static_cast<int>(rank) * BM + quad * 32;
+            constexpr int E = static_cast<int>(sizeof(OutT));
+            constexpr int kPerChunk = 16 / E;                                   // values per 16-byte chunk
+            constexpr int kRoundCols = (kCols * E >= 128) ? 128 / E : kCols;    // columns staged per round
+            constexpr int kChunks = kRoundCols * E / 16;                        // 8, or 4 for 64-byte rows
+            constexpr int kRounds = kCols / kRoundCols;
+            constexpr int kRowBytes = kChunks * 16;
+            OutT* outp = static_cast<OutT*>(out);
             if (vector_store) {
 #pragma unroll
-                for (int g = 0; g < kGroups; ++g) {
-                    const int colg = n0 + col0 + g * 32;
-                    uint8_t* dst = my_store + lane * 128;
+                for (int g = 0; g < kRounds; ++g) {
+                    const int colg = n0 + col0 + g * kRoundCols;
+                    uint8_t* dst = my_store + lane * kRowBytes;
 #pragma unroll
-                    for (int ch = 0; ch < 8; ++ch) {
-                        float4 w;
-                        w.x = __shfl_sync(0xffffffffu, bwreg[0], g * 8 + ch);
-                        w.y = __shfl_sync(0xffffffffu, bwreg[1], g * 8 + ch);
-                        w.z = __shfl_sync(0xffffffffu, bwreg[2], g * 8 + ch);
-                        w.w = __shfl_sync(0xffffffffu, bwreg[3], g * 8 + ch);
-                        float4 o;
-                        o.x = (acc[g * 32 + ch * 4 + 0] * w.x) * scale_inv;
-                        o.y = (acc[g * 32 + ch * 4 + 1] * w.y) * scale_inv;
-                        o.z = (acc[g * 32 + ch * 4 + 2] * w.z) * scale_inv;
-                        o.w = (acc[g * 32 + ch * 4 + 3] * w.w) * scale_inv;
-                        *reinterpret_cast<float4*>(dst + ((ch ^ (lane & 7)) << 4)) = o;
+                    for (int ch = 0; ch < kChunks; ++ch) {
+                        OutT vals[kPerChunk];
+#pragma unroll
+                        for (int e = 0; e < kPerChunk; ++e) {
+                            const int j = g * kRoundCols + ch * kPerChunk + e;
+                            const float w = __shfl_sync(0xffffffffu, bwreg[j & 3], j >> 2);
+                            const float bv = __shfl_sync(0xffffffffu, biasreg[j & 3], j >> 2);
+                            vals[e] = finish<OutT>((acc[j] * w) * scale_inv, bv, has_bias);
+                        }
+                        const int swz = kChunks == 8 ? (ch ^ (lane & 7)) : (ch ^ ((lane >> 1) & 3));
+                        *reinterpret_cast<uint4*>(dst + (swz << 4)) = *reinterpret_cast<const uint4*>(vals);
                     }
                     __syncwarp();
-                    const int cchunk = lane & 7;
-                    const int col = colg + cchunk * 4;
+                    const int cchunk = lane % kChunks;
+                    const int col = colg + cchunk * kPerChunk;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int rr = i * 4 + (lane >> 3);
-                        const float4 o = *reinterpret_cast<const float4*>(my_store + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
+                    for (int i = 0; i < kChunks; ++i) {
+                        const int rr = i * (32 / kChunks) + lane / kChunks;
+                        const int swz = kChunks == 8 ? (cchunk ^ (rr & 7)) : (cchunk ^ ((rr >> 1) & 3));
+                        const uint4 o = *reinterpret_cast<const uint4*>(my_store + rr * kRowBytes + (swz << 4));
                         const int grow = row_base + rr;
-                        if (grow < Q && col < R) {   // R % 4 == 0 on this path, so col < R covers col + 3
-                            *reinterpret_cast<float4*>(out + static_cast<int64_t>(grow) * ldo + col) = o;
+                        if (grow < Q && col < R) {   // R is a multiple of kPerChunk on this path
+                            *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(grow) * ldo + col) = o;
                         }
                     }
                     __syncwarp();
                 }
             } else {
-                float* orow = out + static_cast<int64_t>(row_ok ? row : 0) * ldo;
+                OutT* orow = outp + static_cast<int64_t>(row_ok ? row : 0) * ldo;
 #pragma unroll
                 for (int j = 0; j < kCols; ++j) {
                     const int col = n0 + col0 + j;
                     const float w = __shfl_sync(0xffffffffu, bwreg[j & 3], j >> 2);
-                    if (row_ok && col < R) orow[col] = (acc[j] * w) * scale_inv;
+                    const float bv = __shfl_sync(0xffffffffu, biasreg[j & 3], j >> 2);
+                    if (row_ok && col < R) orow[col] = finish<OutT>((acc[j] * w) * scale_inv, bv, has_bias);
                 }
             }
         }

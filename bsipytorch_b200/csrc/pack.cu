@@ -35,6 +35,40 @@ __device__ __forceinline__ long long round_half_away(double x) {
 
 __device__ __forceinline__ u64 uabs(long long v) { return static_cast<u64>(v >= 0 ? v : -v); }
 
+// half_away(double(f) * 10^dp) in integer arithmetic, bit for bit the value the float64 expression
+// gives. With f = m * 2^e (m < 2^24) and mult = 10^dp < 2^27 the product m * mult has at most 51
+// bits, so the float64 multiply is exact, and so is the + 0.5 before the floor wherever it can change
+// the result; half-away rounding of the exact value is (|P| + 2^(s-1)) >> s. NaN gives 0 and
+// magnitudes of 2^63 or more saturate, which is what the float64 -> int64 conversion does.
+// mult == 0 selects the float64 path (decimal_places outside [0, 8]).
+__device__ __forceinline__ long long decimal_round(float f, double dec_scale, uint32_t mult) {
+    if (mult == 0u) return round_half_away(static_cast<double>(f) * dec_scale);
+    const uint32_t bits = __float_as_uint(f);
+    const uint32_t exp = (bits >> 23) & 0xffu;
+    uint32_t man = bits & 0x7fffffu;
+    const bool neg = (bits >> 31) != 0u;
+    u64 mag;
+    if (exp == 255u) {
+        mag = man ? 0ull : 0x7fffffffffffffffull;
+    } else {
+        int e;
+        if (exp == 0u) {
+            e = -149;
+        } else {
+            man |= 0x800000u;
+            e = static_cast<int>(exp) - 150;
+        }
+        const u64 P = static_cast<u64>(man) * static_cast<u64>(mult);
+        if (e >= 0) {
+            mag = (e >= 63 || (P >> (63 - e)) != 0ull) ? (P ? 0x7fffffffffffffffull : 0ull) : (P << e);
+        } else {
+            const int sh = -e;
+            mag = sh >= 53 ? 0ull : ((P + (1ull << (sh - 1))) >> sh);
+        }
+    }
+    return neg ? -static_cast<long long>(mag) : static_cast<long long>(mag);
+}
+
 __device__ __forceinline__ u64 warp_max_u64(u64 v) {
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -86,22 +120,9 @@ __device__ __forceinline__ void load8(const T* __restrict__ row, int64_t col, in
     }
 }
 
-// Quantises the lane's 8 integers with `shift`, clamps, writes slices and the int8 image.
-__device__ __forceinline__ void emit_chunk(const long long (&v)[8], int shift, int bits, int lane,
-                                           int64_t chunk, int64_t W, u64* __restrict__ words_row,
-                                           int8_t* __restrict__ q8_row) {
-    const long long qmax = (1ll << (bits - 1)) - 1ll;
-    const long long qmin = -(1ll << (bits - 1));
-    const u64 round_add = shift > 0 ? (1ull << (shift - 1)) : 0ull;
-    u64 packed = 0;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const u64 uq = (uabs(v[e]) + round_add) >> shift;
-        long long q = v[e] < 0 ? -static_cast<long long>(uq) : static_cast<long long>(uq);
-        q = q < qmin ? qmin : q;
-        q = q > qmax ? qmax : q;
-        packed |= (static_cast<u64>(q) & 0xffull) << (8 * e);
-    }
+// Writes the lane's 8 clamped values (one byte each in `packed`): int8 image and bit slices.
+__device__ __forceinline__ void store_packed(u64 packed, int bits, int lane, int64_t chunk, int64_t W,
+                                             u64* __restrict__ words_row, int8_t* __restrict__ q8_row) {
     if (q8_row != nullptr) {
         *reinterpret_cast<u64*>(q8_row + chunk * 256 + lane * 8) = packed;
     }
@@ -118,9 +139,38 @@ __device__ __forceinline__ void emit_chunk(const long long (&v)[8], int shift, i
     }
 }
 
+// Quantises the lane's 8 integers with `shift`, clamps, writes slices and the int8 image.
+__device__ __forceinline__ void emit_chunk(const long long (&v)[8], int shift, int bits, int lane,
+                                           int64_t chunk, int64_t W, u64* __restrict__ words_row,
+                                           int8_t* __restrict__ q8_row) {
+    const long long qmax = (1ll << (bits - 1)) - 1ll;
+    const long long qmin = -(1ll << (bits - 1));
+    const u64 round_add = shift > 0 ? (1ull << (shift - 1)) : 0ull;
+    u64 packed = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const u64 uq = (uabs(v[e]) + round_add) >> shift;
+        long long q = v[e] < 0 ? -static_cast<long long>(uq) : static_cast<long long>(uq);
+        q = q < qmin ? qmin : q;
+        q = q > qmax ? qmax : q;
+        packed |= (static_cast<u64>(q) & 0xffull) << (8 * e);
+    }
+    store_packed(packed, bits, lane, chunk, W, words_row, q8_row);
+}
+
+// 32-bit variant of the quantiser for the common case (10^dp <= 127 and every |x| of the warp's chunk
+// below 2^23, so that every product and magnitude fits 32 bits). Same integers as the 64-bit path.
+__device__ __forceinline__ uint32_t decimal_round_mag32(uint32_t fbits, uint32_t mult) {
+    const uint32_t exp = (fbits >> 23) & 0xffu;
+    const uint32_t man = (fbits & 0x7fffffu) | (exp ? 0x800000u : 0u);
+    const uint32_t sh = 150u - exp;  // >= 1 on this path; denormals get sh = 150
+    const uint32_t P = man * mult;   // < 2^31
+    return sh >= 32u ? 0u : ((P + (1u << (sh - 1u))) >> sh);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_chunk_kernel(
-    const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, int bits,
+    const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
     int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
     int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok) {
     const int lane = threadIdx.x & 31;
@@ -131,11 +181,57 @@ __global__ void __launch_bounds__(256) quantize_pack_chunk_kernel(
 
     float f[8];
     load8<T>(x + row * ldx, chunk * 256 + lane * 8, D, vec_ok != 0, f);
+    u64* words_row = words != nullptr ? words + row * bits * W : nullptr;
+    int8_t* q8_row = q8 != nullptr ? q8 + row * ld8 : nullptr;
+
+    bool fast = dec_mult != 0u && dec_mult <= 127u;
+    if (fast) {
+        uint32_t big = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) big |= (((__float_as_uint(f[e]) >> 23) & 0xffu) >= 150u) ? 1u : 0u;
+        fast = !__any_sync(0xffffffffu, big != 0u);
+    }
+    if (fast) {
+        uint32_t mag[8];
+        uint32_t mx32 = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            mag[e] = decimal_round_mag32(__float_as_uint(f[e]), dec_mult);
+            mx32 = mag[e] > mx32 ? mag[e] : mx32;
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const uint32_t o = __shfl_xor_sync(0xffffffffu, mx32, off);
+            mx32 = o > mx32 ? o : mx32;
+        }
+        int shift = (mx32 ? 32 - __clz(static_cast<int>(mx32)) : 0) - (bits - 1);
+        shift = shift < 0 ? 0 : shift;
+        if (lane == 0) {
+            if (scales != nullptr) scales[unit] = static_cast<float>(1u << shift);
+            if (shifts != nullptr) shifts[unit] = shift;
+        }
+        const int qmax = (1 << (bits - 1)) - 1;
+        const int qmin = -(1 << (bits - 1));
+        const uint32_t round_add = shift > 0 ? (1u << (shift - 1)) : 0u;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            int q = static_cast<int>((mag[e] + round_add) >> shift);
+            q = (__float_as_uint(f[e]) >> 31) ? -q : q;
+            q = q > qmax ? qmax : q;
+            q = q < qmin ? qmin : q;                      // a negative value may use the extra level -2^(b-1)
+            const uint32_t byte = static_cast<uint32_t>(q) & 0xffu;
+            if (e < 4) lo |= byte << (8 * e); else hi |= byte << (8 * (e - 4));
+        }
+        store_packed(static_cast<u64>(lo) | (static_cast<u64>(hi) << 32), bits, lane, chunk, W, words_row, q8_row);
+        return;
+    }
+
     long long v[8];
     u64 mx = 0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        v[e] = round_half_away(static_cast<double>(f[e]) * dec_scale);
+        v[e] = decimal_round(f[e], dec_scale, dec_mult);
         const u64 a = uabs(v[e]);
         mx = a > mx ? a : mx;
     }
@@ -145,14 +241,12 @@ __global__ void __launch_bounds__(256) quantize_pack_chunk_kernel(
         if (scales != nullptr) scales[unit] = static_cast<float>(1ull << shift);
         if (shifts != nullptr) shifts[unit] = shift;
     }
-    emit_chunk(v, shift, bits, lane, chunk, W,
-               words != nullptr ? words + row * bits * W : nullptr,
-               q8 != nullptr ? q8 + row * ld8 : nullptr);
+    emit_chunk(v, shift, bits, lane, chunk, W, words_row, q8_row);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
-    const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, int bits,
+    const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
     int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
     int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok) {
     __shared__ u64 warp_max[8];
@@ -167,7 +261,7 @@ __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
         load8<T>(xr, chunk * 256 + lane * 8, D, vec_ok != 0, f);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            const u64 a = uabs(round_half_away(static_cast<double>(f[e]) * dec_scale));
+            const u64 a = uabs(decimal_round(f[e], dec_scale, dec_mult));
             mx = a > mx ? a : mx;
         }
     }
@@ -187,7 +281,7 @@ __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
         load8<T>(xr, chunk * 256 + lane * 8, D, vec_ok != 0, f);
         long long v[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = round_half_away(static_cast<double>(f[e]) * dec_scale);
+        for (int e = 0; e < 8; ++e) v[e] = decimal_round(f[e], dec_scale, dec_mult);
         emit_chunk(v, shift, bits, lane, chunk, W,
                    words != nullptr ? words + row * bits * W : nullptr,
                    q8 != nullptr ? q8 + row * ld8 : nullptr);
@@ -279,6 +373,11 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
     const int esz = dtype == BSI_DTYPE_F32 ? 4 : 2;
     const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && ((ldx * esz) & 15) == 0) ? 1 : 0;
     const double dec_scale = pow(10.0, static_cast<double>(decimal_places));
+    uint32_t dec_mult = 0;  // 10^dp when it is a small integer; 0 = use the float64 expression
+    if (decimal_places >= 0 && decimal_places <= 8) {
+        dec_mult = 1;
+        for (int i = 0; i < decimal_places; ++i) dec_mult *= 10u;
+    }
     u64* w = reinterpret_cast<u64*>(words);
 
 #define BSI_LAUNCH_PACK(T)                                                                        \
@@ -286,11 +385,11 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
         if (chunk_mode) {                                                                         \
             const int64_t blocks = (rows * chunks + 7) / 8;                                       \
             quantize_pack_chunk_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(     \
-                static_cast<const T*>(x), rows, D, ldx, dec_scale, bits, chunks, W, w, scales,    \
+                static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales,    \
                 shifts, q8, ld8, vec_ok);                                                         \
         } else {                                                                                  \
             quantize_pack_row_kernel<T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(         \
-                static_cast<const T*>(x), rows, D, ldx, dec_scale, bits, chunks, W, w, scales,    \
+                static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales,    \
                 shifts, q8, ld8, vec_ok);                                                         \
         }                                                                                         \
     } while (0)

@@ -104,6 +104,17 @@ int bsi_b200_dot_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_s
                     float* out, int64_t ldo, int32_t* dbg_iacc, int engine,
                     bsi_stream_t stream);
 
+/* The dot with the layer epilogue fused in: y[q][r] = cast(out[q][r]) + cast(bias[r]) in y_dtype
+ * (BSI_DTYPE_*), where out is exactly what bsi_b200_dot_i8 would produce; both terms are narrowed
+ * before the add and the sum is narrowed again, as torch does for `scores.to(dtype) + bias.to(dtype)`.
+ * bias may be NULL. Replaces the dot launch plus the two elementwise kernels of
+ * BSIQuantizedLinear.forward (bsi_ops/benchmarks/verify_accuracy_bsi.py:177-195): the float32
+ * [Q, R] intermediate is never written. */
+int bsi_b200_linear_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                       const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                       int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                       void* y, int64_t ldy, int y_dtype, bsi_stream_t stream);
+
 /* Same result computed from the slice words with mma.sync b1 AND+POPC, argument order of the
  * reference launcher (bsi_cuda_kernels_dot.cuh:2616-2635) minus the tile hints and index
  * arrays. Bw is [R, Sb]; only Bw[r][0] = 2^shift_r enters (the slice weights are +-2^j * Bw[r][0],

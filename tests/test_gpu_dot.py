@@ -165,3 +165,34 @@ def test_dot_bad_arguments():
     assert L.bsi_b200_dot_i8(*args(256, 2, 0)) == capi.ERR_INVALID      # ldo < R
     assert L.bsi_b200_dot_i8(*args(256, 4, 3)) == capi.ERR_INVALID      # BMMA engine needs slice words
     assert L.bsi_b200_dot_i8(*args(256, 4, 1032)) == capi.ERR_INVALID   # tile width not 64/128/256
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(512, 1024, 512), (300, 520, 256), (130, 67, 512), (64, 256, 1024)])
+def test_linear_i8_fuses_cast_and_bias(dtype, shape):
+    """y = cast(dot) + cast(bias) from the fused entry point equals dot (float32) followed by the
+    separate cast + bias kernel, which is the reference layer's arithmetic."""
+    import ctypes as C
+    Q, R, D = shape
+    q, k = _inputs.fc1(Q=Q, R=R, D=D, seed=Q * 3 + R, dtype=torch.float32)
+    qa, kb, _ = _prepare(q, k)
+    g = torch.Generator().manual_seed(R)
+    bias = (torch.randn(R, generator=g) * 0.5).to(DEV)
+    out = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), capi.ENGINE_TCGEN05)
+    code = {torch.float32: capi.DTYPE_F32, torch.float16: capi.DTYPE_F16, torch.bfloat16: capi.DTYPE_BF16}[dtype]
+    chunks = D // 256
+    L = capi.lib()
+    for b in (bias, None):
+        want = out.to(dtype) + b.to(dtype) if b is not None else out.to(dtype)
+        if dtype == torch.float32 and b is not None:
+            want = out + b
+        y = torch.full((Q, R), float("nan"), dtype=dtype, device=DEV)
+        rc = L.bsi_b200_linear_i8(capi.ptr(qa["q8"]), qa["q8"].shape[1], capi.ptr(qa["scales"]), chunks,
+                                  capi.ptr(kb["q8"]), kb["q8"].shape[1], capi.ptr(kb["scales"]), capi.ptr(b), Q, R,
+                                  chunks, C.c_float(float(o.scale_inv(2))), capi.ptr(y), R, code, capi.stream_ptr())
+        capi.check(rc, "bsi_b200_linear_i8")
+        assert torch.equal(y, want)
+        y2 = torch.empty_like(y)
+        capi.check(L.bsi_b200_cast_bias(capi.ptr(out), R, capi.ptr(b), Q, R, capi.ptr(y2), R, code, capi.stream_ptr()))
+        assert torch.equal(y2, want)
+    assert capi.device_status() == 0
