@@ -131,9 +131,11 @@ __device__ __forceinline__ void store_packed(u64 packed, int bits, int lane, int
         if (word < W) {
             const u64 t = transpose8x8(packed);
             uint8_t* dst = reinterpret_cast<uint8_t*>(words_row + word) + (lane & 7);
-            for (int s = 0; s < bits; ++s) {
-                dst[static_cast<size_t>(s) * static_cast<size_t>(W) * 8u] =
-                    static_cast<uint8_t>(t >> (8 * s));
+            const uint32_t tl = static_cast<uint32_t>(t), th = static_cast<uint32_t>(t >> 32);
+            const size_t step = static_cast<size_t>(W) * 8u;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                if (s < bits) dst[s * step] = static_cast<uint8_t>((s < 4 ? tl : th) >> (8 * (s & 3)));
             }
         }
     }
@@ -168,65 +170,51 @@ __device__ __forceinline__ uint32_t decimal_round_mag32(uint32_t fbits, uint32_t
     return sh >= 32u ? 0u : ((P + (1u << (sh - 1u))) >> sh);
 }
 
+// prmt.b32 with the full 4-bit selectors (values 8..15 replicate the sign bit of the chosen byte over the
+// result byte; the __byte_perm intrinsic only honours 3 bits per selector).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+// Byte-wise tail of the fast paths: u[e] carries the unsigned quantised magnitude of element e in its
+// low byte (0 .. 2^(bits-1)), f[e] the sign. Clamps positives to 2^(bits-1)-1, negates the negatives and
+// returns the 8 two's-complement bytes, four elements per 32-bit register operation.
+__device__ __forceinline__ u64 sign_clamp_bytes(const uint32_t (&u)[8], const float (&f)[8], int bits) {
+    const uint32_t top = 0x01010101u << (bits - 1);
+    uint32_t out[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int e = 4 * h;
+        // low bytes of u[e..e+3]
+        uint32_t w = __byte_perm(__byte_perm(u[e], u[e + 1], 0x0040), __byte_perm(u[e + 2], u[e + 3], 0x0040), 0x5410);
+        // 0xff per negative element
+        const uint32_t m = prmt(prmt(__float_as_uint(f[e]), __float_as_uint(f[e + 1]), 0x00fbu),
+                                prmt(__float_as_uint(f[e + 2]), __float_as_uint(f[e + 3]), 0x00fbu), 0x5410u);
+        // positive 2^(bits-1) -> 2^(bits-1) - 1 (the byte is exactly `top` there, so the borrow stays inside it)
+        const uint32_t over = w & ~m & top;
+        w -= over >> (bits - 1);
+        // negate the bytes under m: (~b + 1) per byte, the carry kept inside the byte by adding in 7 bits
+        const uint32_t x = w ^ m;
+        const uint32_t t = (x & 0x7f7f7f7fu) + (m & 0x01010101u);
+        out[h] = t ^ (x & 0x80808080u);
+    }
+    return static_cast<u64>(out[0]) | (static_cast<u64>(out[1]) << 32);
+}
+
+// One (row, chunk) unit on the generic path (any decimal_places, any magnitude, NaN/inf, any layout):
+// 64-bit integers and 64-bit offsets throughout.
 template <typename T>
-__global__ void __launch_bounds__(256) quantize_pack_chunk_kernel(
-    const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
-    int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
-    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok) {
-    const int lane = threadIdx.x & 31;
-    const int64_t unit = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-    if (unit >= rows * chunks) return;
+__device__ __forceinline__ void generic_unit(const T* __restrict__ x, int64_t unit, int64_t D, int64_t ldx,
+                                             double dec_scale, uint32_t dec_mult, int bits, int64_t chunks, int64_t W,
+                                             u64* __restrict__ words, float* __restrict__ scales,
+                                             int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8,
+                                             bool vec, int lane) {
     const int64_t row = unit / chunks;
     const int64_t chunk = unit - row * chunks;
-
     float f[8];
-    load8<T>(x + row * ldx, chunk * 256 + lane * 8, D, vec_ok != 0, f);
-    u64* words_row = words != nullptr ? words + row * bits * W : nullptr;
-    int8_t* q8_row = q8 != nullptr ? q8 + row * ld8 : nullptr;
-
-    bool fast = dec_mult != 0u && dec_mult <= 127u;
-    if (fast) {
-        uint32_t big = 0;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) big |= (((__float_as_uint(f[e]) >> 23) & 0xffu) >= 150u) ? 1u : 0u;
-        fast = !__any_sync(0xffffffffu, big != 0u);
-    }
-    if (fast) {
-        uint32_t mag[8];
-        uint32_t mx32 = 0;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            mag[e] = decimal_round_mag32(__float_as_uint(f[e]), dec_mult);
-            mx32 = mag[e] > mx32 ? mag[e] : mx32;
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const uint32_t o = __shfl_xor_sync(0xffffffffu, mx32, off);
-            mx32 = o > mx32 ? o : mx32;
-        }
-        int shift = (mx32 ? 32 - __clz(static_cast<int>(mx32)) : 0) - (bits - 1);
-        shift = shift < 0 ? 0 : shift;
-        if (lane == 0) {
-            if (scales != nullptr) scales[unit] = static_cast<float>(1u << shift);
-            if (shifts != nullptr) shifts[unit] = shift;
-        }
-        const int qmax = (1 << (bits - 1)) - 1;
-        const int qmin = -(1 << (bits - 1));
-        const uint32_t round_add = shift > 0 ? (1u << (shift - 1)) : 0u;
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            int q = static_cast<int>((mag[e] + round_add) >> shift);
-            q = (__float_as_uint(f[e]) >> 31) ? -q : q;
-            q = q > qmax ? qmax : q;
-            q = q < qmin ? qmin : q;                      // a negative value may use the extra level -2^(b-1)
-            const uint32_t byte = static_cast<uint32_t>(q) & 0xffu;
-            if (e < 4) lo |= byte << (8 * e); else hi |= byte << (8 * (e - 4));
-        }
-        store_packed(static_cast<u64>(lo) | (static_cast<u64>(hi) << 32), bits, lane, chunk, W, words_row, q8_row);
-        return;
-    }
-
+    load8<T>(x + row * ldx, chunk * 256 + lane * 8, D, vec, f);
     long long v[8];
     u64 mx = 0;
 #pragma unroll
@@ -241,7 +229,215 @@ __global__ void __launch_bounds__(256) quantize_pack_chunk_kernel(
         if (scales != nullptr) scales[unit] = static_cast<float>(1ull << shift);
         if (shifts != nullptr) shifts[unit] = shift;
     }
-    emit_chunk(v, shift, bits, lane, chunk, W, words_row, q8_row);
+    emit_chunk(v, shift, bits, lane, chunk, W, words != nullptr ? words + row * bits * W : nullptr,
+               q8 != nullptr ? q8 + row * ld8 : nullptr);
+}
+
+// Chunk mode without preconditions: one warp per unit, grid-stride.
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_pack_chunk_generic_kernel(
+    const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
+    int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
+    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok) {
+    const int lane = threadIdx.x & 31;
+    const int64_t total = rows * chunks;
+    for (int64_t unit = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); unit < total;
+         unit += static_cast<int64_t>(gridDim.x) * 8)
+        generic_unit<T>(x, unit, D, ldx, dec_scale, dec_mult, bits, chunks, W, words, scales, shifts, q8, ld8,
+                        vec_ok != 0, lane);
+}
+
+// Fast path of one chunk: true when the chunk was quantised and stored, false when it needs the generic
+// path (some |x * 10^dp| >= 2^23, NaN or inf). Same integers as the generic path, far fewer instructions.
+//
+//  * 16-bit inputs, 10^dp <= 1000: an 11-bit (8-bit for bfloat16) significand times a 10-bit constant
+//    has at most 21 bits, so y = |x| * 10^dp and y + 0.5 are exact in float32. Adding 2^23 with
+//    round-toward-zero leaves 2^23 + floor(y + 0.5) = 2^23 + |v| (floats in [2^23, 2^24) are the
+//    integers). The second rounding (|v| + 2^(s-1)) >> s = floor(|v| * 2^-s + 0.5) is the same step
+//    again: u = fma(r1, 2^-s, 0.5 - 2^(23-s)) is exact and its 2^23-truncation carries the result in the
+//    low mantissa byte. All of this runs on the FMA pipe.
+//  * float32 inputs, 10^dp <= 127: 32-bit integer arithmetic on the float's bit pattern.
+template <typename T, bool kWords, bool kQ8>
+__device__ __forceinline__ bool fast_chunk(const float (&f)[8], uint32_t unit, uint32_t q8_off, uint32_t word_off,
+                                           bool word_ok, int lane, uint32_t dec_mult, int bits, uint32_t slice_bytes,
+                                           u64* __restrict__ words, float* __restrict__ scales,
+                                           int32_t* __restrict__ shifts, int8_t* __restrict__ q8) {
+    uint32_t amax_bits = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) amax_bits = max(amax_bits, __float_as_uint(f[e]) & 0x7fffffffu);
+    amax_bits = __reduce_max_sync(0xffffffffu, amax_bits);   // NaN and inf order above every finite value
+
+    int shift;
+    uint32_t u[8];
+    if constexpr (sizeof(T) == 2) {
+        const float fmult = static_cast<float>(dec_mult);
+        const float ymax = __uint_as_float(amax_bits) * fmult;
+        if (!(amax_bits < 0x7f800000u && ymax < 8388608.0f)) return false;
+        const uint32_t mx = __float2uint_rz(ymax + 0.5f);   // rounding is monotonic: the largest |v|
+        shift = (32 - __clz(static_cast<int>(mx))) - (bits - 1);
+        shift = shift < 0 ? 0 : shift;
+        const float inv = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);   // 2^-shift
+        const float c = (shift > 0 ? 0.5f : 0.0f) - 8388608.0f * inv;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float r1 = __fadd_rz(fmaf(fabsf(f[e]), fmult, 0.5f), 8388608.0f);
+            u[e] = __float_as_uint(__fadd_rz(fmaf(r1, inv, c), 8388608.0f));
+        }
+    } else {
+        if (!(amax_bits < (150u << 23))) return false;
+        const uint32_t mx = decimal_round_mag32(amax_bits, dec_mult);
+        shift = (32 - __clz(static_cast<int>(mx))) - (bits - 1);
+        shift = shift < 0 ? 0 : shift;
+        const uint32_t round_add = shift > 0 ? (1u << (shift - 1)) : 0u;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            u[e] = (decimal_round_mag32(__float_as_uint(f[e]), dec_mult) + round_add) >> shift;
+    }
+    if (lane == 0) {
+        scales[unit] = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);   // 2^shift
+        if (shifts != nullptr) shifts[unit] = shift;
+    }
+    const u64 packed = sign_clamp_bytes(u, f, bits);
+    if constexpr (kQ8) *reinterpret_cast<u64*>(q8 + q8_off) = packed;
+    if constexpr (kWords) {
+        if (word_ok) {
+            const u64 t = transpose8x8(packed);
+            const uint32_t tl = static_cast<uint32_t>(t), th = static_cast<uint32_t>(t >> 32);
+            uint8_t* out = reinterpret_cast<uint8_t*>(words);
+            uint32_t off = word_off;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                if (s < bits) out[off] = static_cast<uint8_t>((s < 4 ? tl : th) >> (8 * (s & 3)));
+                off += slice_bytes;
+            }
+        }
+    }
+    return true;
+}
+
+// Raw 16-byte vectors holding a lane's 8 elements (one for 16-bit types, two for float32). Keeping
+// the next unit's data in this form lets its load stay in flight while the current unit is processed.
+template <typename T>
+struct RawLane {
+    static constexpr int kVecs = sizeof(T) == 2 ? 1 : 2;
+    uint4 v[kVecs];
+    __device__ __forceinline__ void load(const T* __restrict__ p) {
+#pragma unroll
+        for (int i = 0; i < kVecs; ++i) v[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+    }
+    __device__ __forceinline__ void to_floats(float (&f)[8]) const {
+        if constexpr (sizeof(T) == 2) {
+            const T* h = reinterpret_cast<const T*>(&v[0]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = to_float(h[e]);
+        } else {
+            const float* g = reinterpret_cast<const float*>(&v[0]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = g[e];
+        }
+    }
+};
+
+#ifndef BSI_PACK_MIN_BLOCKS
+#define BSI_PACK_MIN_BLOCKS 4
+#endif
+
+// Geometry of a fast chunk-mode launch; the host checks that every offset fits 32 bits.
+struct FastGeom {
+    uint32_t total, chunks, D, ldx, ld8, W;
+    uint32_t row_bytes;     // bits * W * 8: bytes of one row's slices
+    uint32_t slice_bytes;   // W * 8
+};
+
+constexpr int kSlowQueue = 8;   // units per warp that may wait for the generic path
+
+// Persistent fast chunk kernel. The grid is sized to what is resident at once and every warp walks the
+// (row, chunk) units with stride gridDim.x * 8, loading its next unit before it processes the current one
+// (the loop is written out twice so that the two register buffers swap roles without copies). Units the
+// fast path cannot take are queued and redone on the generic path after the loop, which keeps the 64-bit
+// code out of the loop's register budget; a warp whose queue overflows redoes all of its units.
+// kDense: x and q8 are contiguous (ldx == ld8 == D), D is a multiple of 256 and x is 16-byte aligned, so
+// a unit's element offset is unit * 256 and no lane ever needs the scalar tail loads.
+template <typename T, bool kDense, bool kWords, bool kQ8>
+__global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_chunk_fast_kernel(
+    const T* __restrict__ x, FastGeom g, double dec_scale, uint32_t dec_mult, int bits,
+    u64* __restrict__ words, float* __restrict__ scales, int32_t* __restrict__ shifts, int8_t* __restrict__ q8,
+    int vec_ok) {
+    __shared__ uint32_t slow_queue[8][kSlowQueue];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const uint32_t stride = gridDim.x * 8u;
+    const uint32_t first = blockIdx.x * 8u + warp;
+    if (first >= g.total) return;
+    constexpr bool kRows = !kDense || kWords;   // row / chunk are needed, not just the unit number
+    const uint32_t stride_rows = kRows ? stride / g.chunks : 0u;
+    const uint32_t stride_chunks = kRows ? stride - stride_rows * g.chunks : 0u;
+    const bool vec = kDense || vec_ok != 0;
+    const uint32_t lane_col = lane * 8u;
+    const uint32_t lane_word = (lane >> 3) * 8u + (lane & 7u);   // byte within the chunk's 4 words
+    int nslow = 0;
+
+    struct Pos { uint32_t unit, row, chunk; };
+    auto advance = [&](Pos p) {
+        p.unit += stride;
+        if constexpr (kRows) {
+            p.row += stride_rows; p.chunk += stride_chunks;
+            if (p.chunk >= g.chunks) { p.chunk -= g.chunks; ++p.row; }
+        }
+        return p;
+    };
+    auto lane_vec = [&](const Pos& p) { return kDense || (vec && p.chunk * 256u + lane_col + 8u <= g.D); };
+    auto fetch = [&](RawLane<T>& r, const Pos& p) {
+        if constexpr (kDense) r.load(x + (p.unit * 256u + lane_col));
+        else if (lane_vec(p)) r.load(x + (p.row * g.ldx + p.chunk * 256u + lane_col));
+    };
+    auto process = [&](const RawLane<T>& r, const Pos& p) {
+        float f[8];
+        if (lane_vec(p)) r.to_floats(f);
+        else load8<T>(x + static_cast<int64_t>(p.row) * g.ldx, static_cast<int64_t>(p.chunk) * 256 + lane_col,
+                      static_cast<int64_t>(g.D), false, f);
+        const uint32_t q8_off = kDense ? p.unit * 256u + lane_col : p.row * g.ld8 + p.chunk * 256u + lane_col;
+        const uint32_t word_off = kWords ? p.row * g.row_bytes + p.chunk * 32u + lane_word : 0u;
+        const bool word_ok = kDense || p.chunk * 4u + (lane >> 3) < g.W;
+        if (!fast_chunk<T, kWords, kQ8>(f, p.unit, q8_off, word_off, word_ok, lane, dec_mult, bits, g.slice_bytes,
+                                        words, scales, shifts, q8)) {
+            if (nslow < kSlowQueue && lane == 0) slow_queue[warp][nslow] = p.unit;
+            ++nslow;
+        }
+    };
+
+    Pos cur;
+    cur.unit = first;
+    cur.row = kRows ? first / g.chunks : 0u;
+    cur.chunk = kRows ? first - cur.row * g.chunks : 0u;
+    RawLane<T> a, b;
+    fetch(a, cur);
+    for (;;) {
+        Pos nxt = advance(cur);
+        bool more = nxt.unit < g.total;
+        if (more) fetch(b, nxt);
+        process(a, cur);
+        if (!more) break;
+        cur = nxt;
+        nxt = advance(cur);
+        more = nxt.unit < g.total;
+        if (more) fetch(a, nxt);
+        process(b, cur);
+        if (!more) break;
+        cur = nxt;
+    }
+    if (nslow == 0) return;
+    __syncwarp();
+    const int64_t ld8 = kDense ? g.D : g.ld8;
+    if (nslow <= kSlowQueue) {
+        for (int i = 0; i < nslow; ++i)
+            generic_unit<T>(x, slow_queue[warp][i], g.D, g.ldx, dec_scale, dec_mult, bits, g.chunks, g.W, words, scales,
+                            shifts, q8, ld8, vec, lane);
+    } else {
+        for (uint32_t unit = first; unit < g.total; unit += stride)
+            generic_unit<T>(x, unit, g.D, g.ldx, dec_scale, dec_mult, bits, g.chunks, g.W, words, scales, shifts, q8,
+                            ld8, vec, lane);
+    }
 }
 
 template <typename T>
@@ -351,6 +547,94 @@ __global__ void __launch_bounds__(256) cast_bias_kernel(const float* __restrict_
 }  // namespace
 }  // namespace bsi
 
+namespace bsi {
+namespace {
+// Blocks of 256 threads of `kernel` that fit the current device at once (cached per kernel).
+template <typename K>
+int64_t resident_blocks(K kernel) {
+    static thread_local int cached_dev = -1;
+    static thread_local K cached_fn = nullptr;
+    static thread_local int cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { set_error("quantize_pack: cudaGetDevice failed"); return -1; }
+    if (dev != cached_dev || kernel != cached_fn) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm <= 0) {
+            set_error("quantize_pack: occupancy query failed");
+            return -1;
+        }
+        cached = per_sm * sm_count();
+        cached_dev = dev;
+        cached_fn = kernel;
+    }
+    return cached;
+}
+struct ChunkArgs {
+    int64_t rows, D, ldx, ld8, chunks, W;
+    double dec_scale;
+    uint32_t dec_mult;
+    int bits;
+    u64* words;
+    float* scales;
+    int32_t* shifts;
+    int8_t* q8;
+    int vec_ok;
+    cudaStream_t stream;
+};
+
+template <typename T, bool kDense, bool kWords, bool kQ8>
+int launch_chunk_fast(const T* x, const ChunkArgs& a) {
+    const int64_t resident = resident_blocks(quantize_pack_chunk_fast_kernel<T, kDense, kWords, kQ8>);
+    if (resident <= 0) return BSI_ERR_CUDA;
+    int64_t blocks = (a.rows * a.chunks + 7) / 8;
+    blocks = blocks < resident ? blocks : resident;
+    FastGeom g;
+    g.total = static_cast<uint32_t>(a.rows * a.chunks);
+    g.chunks = static_cast<uint32_t>(a.chunks);
+    g.D = static_cast<uint32_t>(a.D);
+    g.ldx = static_cast<uint32_t>(a.ldx);
+    g.ld8 = static_cast<uint32_t>(kQ8 ? a.ld8 : 0);
+    g.W = static_cast<uint32_t>(a.W);
+    g.row_bytes = static_cast<uint32_t>(a.bits * a.W * 8);
+    g.slice_bytes = static_cast<uint32_t>(a.W * 8);
+    quantize_pack_chunk_fast_kernel<T, kDense, kWords, kQ8><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
+        x, g, a.dec_scale, a.dec_mult, a.bits, a.words, a.scales, a.shifts, a.q8, a.vec_ok);
+    return BSI_OK;
+}
+
+// Chunk mode: the fast kernel when its preconditions hold (10^dp small enough for the input type, scales
+// wanted, every offset below 2^31), else the generic kernel.
+template <typename T>
+int launch_chunk(const T* x, const ChunkArgs& a) {
+    int64_t widest = a.chunks * 256;
+    if (a.ldx > widest) widest = a.ldx;
+    if (a.q8 != nullptr && a.ld8 > widest) widest = a.ld8;
+    const uint32_t mult_limit = sizeof(T) == 2 ? 1000u : 127u;
+    const bool fast = a.dec_mult != 0u && a.dec_mult <= mult_limit && a.scales != nullptr &&
+                      a.rows * widest < (1ll << 31) && (a.words != nullptr || a.q8 != nullptr);
+    if (!fast) {
+        int64_t blocks = (a.rows * a.chunks + 7) / 8;
+        const int64_t cap = static_cast<int64_t>(sm_count()) * 64;
+        blocks = blocks < cap ? blocks : cap;
+        quantize_pack_chunk_generic_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
+            x, a.rows, a.D, a.ldx, a.dec_scale, a.dec_mult, a.bits, a.chunks, a.W, a.words, a.scales, a.shifts, a.q8,
+            a.ld8, a.vec_ok);
+        return BSI_OK;
+    }
+    const bool dense = a.vec_ok && a.ldx == a.D && (a.D & 255) == 0 && (a.q8 == nullptr || a.ld8 == a.D);
+    const bool w = a.words != nullptr, q = a.q8 != nullptr;
+    if (dense) {
+        if (w && q) return launch_chunk_fast<T, true, true, true>(x, a);
+        if (q) return launch_chunk_fast<T, true, false, true>(x, a);
+        return launch_chunk_fast<T, true, true, false>(x, a);
+    }
+    if (w && q) return launch_chunk_fast<T, false, true, true>(x, a);
+    if (q) return launch_chunk_fast<T, false, false, true>(x, a);
+    return launch_chunk_fast<T, false, true, false>(x, a);
+}
+}  // namespace
+}  // namespace bsi
+
 extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
                                       int decimal_places, int bits, int chunk_mode,
                                       uint64_t* words, float* scales, int32_t* shifts,
@@ -380,26 +664,23 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
     }
     u64* w = reinterpret_cast<u64*>(words);
 
-#define BSI_LAUNCH_PACK(T)                                                                        \
-    do {                                                                                          \
-        if (chunk_mode) {                                                                         \
-            const int64_t blocks = (rows * chunks + 7) / 8;                                       \
-            quantize_pack_chunk_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(     \
-                static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales,    \
-                shifts, q8, ld8, vec_ok);                                                         \
-        } else {                                                                                  \
-            quantize_pack_row_kernel<T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(         \
-                static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales,    \
-                shifts, q8, ld8, vec_ok);                                                         \
-        }                                                                                         \
-    } while (0)
-
-    if ((chunk_mode ? (rows * chunks + 7) / 8 : rows) > 0x7fffffffll)
-        return fail(BSI_ERR_UNSUPPORTED, "quantize_pack: too many rows for one launch");
-    if (dtype == BSI_DTYPE_F32) BSI_LAUNCH_PACK(float);
-    else if (dtype == BSI_DTYPE_F16) BSI_LAUNCH_PACK(__half);
-    else BSI_LAUNCH_PACK(__nv_bfloat16);
-#undef BSI_LAUNCH_PACK
+    if (chunk_mode) {
+        ChunkArgs a{rows, D, ldx, ld8, chunks, W, dec_scale, dec_mult, bits, w, scales, shifts, q8, vec_ok, stream};
+        int rc;
+        if (dtype == BSI_DTYPE_F32) rc = launch_chunk<float>(static_cast<const float*>(x), a);
+        else if (dtype == BSI_DTYPE_F16) rc = launch_chunk<__half>(static_cast<const __half*>(x), a);
+        else rc = launch_chunk<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(x), a);
+        if (rc != BSI_OK) return rc;
+    } else {
+        if (rows > 0x7fffffffll) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack: too many rows for one launch");
+#define BSI_LAUNCH_ROW(T)                                                                              \
+    quantize_pack_row_kernel<T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(                      \
+        static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales, shifts, q8, ld8, vec_ok)
+        if (dtype == BSI_DTYPE_F32) BSI_LAUNCH_ROW(float);
+        else if (dtype == BSI_DTYPE_F16) BSI_LAUNCH_ROW(__half);
+        else BSI_LAUNCH_ROW(__nv_bfloat16);
+#undef BSI_LAUNCH_ROW
+    }
     return check_launch("quantize_pack launch");
 }
 

@@ -54,6 +54,34 @@ def test_pack_other_decimal_places(dp):
     _check(torch.randn(6, 512, generator=g), 7, True, dp=dp)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_pack_mixes_fast_and_generic_chunks(dtype):
+    """Chunks holding huge, infinite or NaN values leave the fast quantiser for the 64-bit one; their
+    neighbours stay on the fast one. Both give the checker's integers."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(40, 1024, generator=g)
+    big = 6.0e4 if dtype == torch.float16 else 3.0e7      # x100 reaches 2^23 either way
+    x[1, 5] = big
+    x[2, 300] = -big
+    x[3, 600] = float("inf")
+    x[4, 1000] = float("-inf")
+    x[5, 0] = float("nan")
+    x[6, 256:512] = big
+    x[7] = big
+    _check(x.to(dtype), 7, True)
+    _check(x.to(dtype), 6, False)
+
+
+def test_pack_generic_queue_overflow():
+    """More generic-path chunks than one warp can queue: the warp redoes all of its chunks."""
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(5000, 2048, generator=g)
+    x[:, ::256] = 1.0e6                                   # every chunk of every row is out of fast range
+    x[::7] = torch.randn(2048, generator=g)               # ... except the rows left plain
+    _check(x, 7, True)
+    _check(x.to(torch.bfloat16), 7, True)
+
+
 def test_pack_config_distributions():
     q, k = _inputs.fc1(Q=64, R=96)
     _check(q, 7, True)
