@@ -242,7 +242,24 @@ def run_opt(args, rank, world, local_rank):
     cfg = opt.CONFIGS[args.workload]
     B, T = spec["batch"], spec["seq"]
     dtype = getattr(torch, spec["dtype"])
-    model = opt.build_opt_bsi(args.workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world)
+    if args.opt_impl == "tp":
+        # fused QKV key set, head-sharded attention, token-sharded residual stream, packed int8 exchanges
+        from bsipytorch_b200.opt_tp import build_opt_tp
+        model = build_opt_tp(args.workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world,
+                             exchange=args.exchange)
+        graphed = bool(args.cuda_graph) and (world == 1 or model.exchange == "peer")
+        if graphed:
+            model.capture(spec["batch"], spec["seq"])
+        launches_per_layer = 8 if world == 1 else 14      # 4 activation packs + 4 fused linears (+ 6 flag barriers)
+        scheme = ("tensor parallel: R-sharded BSI linears, head-sharded attention, token-sharded residual; packed int8 "
+                  "activations and linear outputs " + ("stored straight into peer buffers over NVLink by the pack / linear kernels"
+                                                       if model.exchange == "peer" else "moved by NCCL all-gather / all-to-all"))
+    else:
+        # one BSIQuantizedLinear per nn.Linear, each followed by an fp16 all-gather of its outputs
+        model = opt.build_opt_bsi(args.workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world)
+        launches_per_layer = 12     # 6 x (pack + fused linear)
+        graphed = False
+        scheme = "R-sharded BSI linears + fp16 all-gather of every output"
     ids_host = torch.randint(0, cfg.vocab_size, (B, T), generator=torch.Generator().manual_seed(0)).pin_memory()
     ids = ids_host.to(dev)
     tok_host = torch.empty(B, dtype=torch.long).pin_memory()
@@ -295,12 +312,13 @@ def run_opt(args, rank, world, local_rank):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 BSI linears, fp16 elsewhere",
             "data": "synthetic",
             "config": {"workload": f"{args.workload} random init, batch {B} x seq {T} uniform random ids, all q/k/v/out/fc1/fc2 as BSI ops, dp=2, fixed76 chunkscale",
-                       "parallelism": f"R-sharded BSI linears + all-gather x{world}" if world > 1 else "1 GPU",
+                       "parallelism": f"{scheme} x{world}" if world > 1 else "1 GPU",
+                       "model_impl": args.opt_impl, "launch": "CUDA graph of the decoder stack" if graphed else "eager",
                        "l2": "weights and activations of one forward exceed the 126 MiB L2" if args.workload != "opt-125m" else "keys of one forward (~150 MB with slices) are about the size of L2"},
             "e2e": {"value": B * T * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8,
                     "d2h_bytes_per_step": B * 8, "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
                     "path": "pinned host ids -> H2D -> OPTForCausalLM.next_token (BSI linears) -> D2H argmax tokens"},
-            "gpu_launches": K * L * 6 * 3,
+            "gpu_launches": K * L * launches_per_layer,
             "clocks": sampler.summary(),
             "roofline": {"bound": "tensor", "achieved": tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": tops / int8_peak,
                          "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16']}", "traffic": None,
@@ -318,6 +336,11 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4000)
     ap.add_argument("--warmup", type=int, default=40)
+    ap.add_argument("--opt-impl", default="tp", choices=["tp", "layers"],
+                    help="OPT workloads: tensor-parallel decoder (default) or one BSIQuantizedLinear per nn.Linear")
+    ap.add_argument("--cuda-graph", type=int, default=1, help="tensor-parallel OPT: replay the decoder stack from a CUDA graph")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "collective"],
+                    help="tensor-parallel OPT: peer-memory stores (default on GPUs) or NCCL collectives")
     ap.add_argument("--workload", default="fc1", choices=sorted(WORKLOADS) + sorted(OPT_WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=30)

@@ -27,7 +27,7 @@ LIB = os.path.join(PKG, "libbsi_b200.so")
 EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
 EXT = os.path.join(PKG, "bsi_ops" + EXT_SUFFIX)
 
-CUDA_SOURCES = ["common.cu", "pack.cu", "ewah.cu", "dot.cu", "dot_tcgen05.cu", "dot_bmma.cu"]
+CUDA_SOURCES = ["common.cu", "pack.cu", "ewah.cu", "dot.cu", "dot_tcgen05.cu", "dot_bmma.cu", "peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

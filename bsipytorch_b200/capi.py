@@ -28,6 +28,14 @@ SIGNATURES = {
     "bsi_b200_recombine_i8": (_i32, [_vp, _i64, _i32, _i64, _vp, _i64, _vp]),
     "bsi_b200_dot_i8": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i32, _vp]),
     "bsi_b200_linear_i8": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _i32, _vp]),
+    "bsi_b200_linear_i8_act": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _i32, _i32, _vp]),
+    "bsi_b200_linear_i8_scatter": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp, _i64, _i64, _i32, _i32, _vp]),
+    "bsi_b200_quantize_pack_multi": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _vp]),
+    "bsi_b200_peer_alloc": (_i32, [_i64, _vp, _vp]),
+    "bsi_b200_peer_free": (_i32, [_vp]),
+    "bsi_b200_peer_open": (_i32, [_vp, _vp]),
+    "bsi_b200_peer_close": (_i32, [_vp]),
+    "bsi_b200_peer_barrier": (_i32, [_vp, _i32, _i32, _i64, _vp]),
     "bsi_b200_dot_words": (_i32, [_vp, _vp, _i64, _i32, _i64, _vp, _vp, _i32, _i64, _i64, _f32, _i64, _vp, _vp, _vp]),
     "bsi_b200_ewah_flags": (_i32, [_vp, _i64, _i64, _f64, _vp, _vp, _vp]),
     "bsi_b200_ewah_size": (_i32, [_vp, _i64, _i64, _vp, _vp, _vp]),

@@ -9,6 +9,7 @@
 // set to reach this path (its README's fixed76 recipe); here they are the defaults. The
 // variable-slice mode (bits = 0), which needs the un-vendored bsiCPP key builder, is rejected.
 #include <torch/extension.h>
+#include <pybind11/stl.h>
 
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -532,6 +533,157 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
     return y;
 }
 
+// Quantise + pack activations (query side: chunk scales) into tensors the caller owns: q8 [rows, >= d]
+// int8 (any row stride that is a multiple of 16 bytes, e.g. a column block of a wider matrix) and
+// scales [rows, d/256] float32, contiguous. This is the first half of bsi_linear_forward, split off so
+// that a tensor-parallel layer can pack its own column block straight into the buffer the ranks
+// exchange. d must be a multiple of 256.
+void pack_queries_into(torch::Tensor x2d, torch::Tensor q8, torch::Tensor scales, int decimalPlaces) {
+    TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
+    TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [rows, d]");
+    TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
+    check_clip();
+    TORCH_CHECK(chunk_scale_enabled(), "pack_queries_into needs BSI_FIXED_CHUNK_SCALE=1");
+    at::Tensor x = x2d.detach();
+    if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
+        x = x.to(at::kFloat);
+    if (x.stride(1) != 1) x = x.contiguous();
+    const int64_t rows = x.size(0), d = x.size(1);
+    TORCH_CHECK(d % 256 == 0, "d must be a multiple of 256");
+    TORCH_CHECK(q8.size(0) == rows && q8.size(1) >= d, "q8 shape mismatch");
+    TORCH_CHECK(scales.numel() == rows * (d / 256), "scales shape mismatch");
+    if (rows == 0 || d == 0) return;
+    check_status(bsi_b200_quantize_pack(x.data_ptr(), dtype_code(x), rows, d, x.stride(0), decimalPlaces,
+                                        bits_queries(), 1, nullptr, scales.data_ptr<float>(), nullptr,
+                                        q8.data_ptr<int8_t>(), q8.stride(0), current_stream()),
+                 "bsi_b200_quantize_pack");
+}
+
+// Second half of bsi_linear_forward: the dot of already packed activations with a key set, cast to
+// `out_dtype`, bias added, optionally ReLU. q8 [Q, d] int8 (row stride a multiple of 16), scales
+// [Q, d/256] float32 contiguous.
+at::Tensor linear_from_packed(torch::Tensor q8, torch::Tensor scales, py::capsule keyset_cuda_cap,
+                              c10::optional<torch::Tensor> bias, int decimalPlaces, py::object out_dtype, bool relu) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
+    TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
+    const int64_t Q = q8.size(0), R = keys->num_keys, chunks = keys->b.chunks;
+    TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
+    TORCH_CHECK(q8.size(1) == chunks * 256, "Word count mismatch between query batch and keys");
+    TORCH_CHECK(scales.numel() == Q * chunks, "scales shape mismatch");
+    TORCH_CHECK(decimalPlaces == keys->b.decimals, "Decimal mismatch between queries and keys: q=", decimalPlaces,
+                " k=", keys->b.decimals);
+    const int total_decimals = decimalPlaces + keys->b.decimals;
+    const double scale_inv = total_decimals > 0 ? 1.0 / std::pow(10.0, total_decimals) : 1.0;
+    const at::ScalarType yt = torch::python::detail::py_object_to_dtype(out_dtype);
+    TORCH_CHECK(yt == at::kFloat || yt == at::kHalf || yt == at::kBFloat16, "out_dtype must be float32, float16 or bfloat16");
+    at::Tensor y = at::empty({Q, R}, q8.options().dtype(yt));
+    const float* bptr = nullptr;
+    at::Tensor b32;
+    if (bias.has_value() && bias->defined()) {
+        b32 = bias->to(y.device(), at::kFloat).contiguous();
+        TORCH_CHECK(b32.numel() == R, "bias length mismatch");
+        bptr = b32.data_ptr<float>();
+    }
+    const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
+    check_status(bsi_b200_linear_i8_act(q8.data_ptr<int8_t>(), q8.stride(0), scales.data_ptr<float>(), chunks,
+                                        keys->b.q8.data_ptr<int8_t>(), keys->b.q8.size(1), keys->b.scales.data_ptr<float>(),
+                                        bptr, Q, R, chunks, static_cast<float>(scale_inv), y.data_ptr(), R, code,
+                                        relu ? BSI_ACT_RELU : BSI_ACT_NONE, current_stream()),
+                 "bsi_b200_linear_i8_act");
+    return y;
+}
+
+// ---- peer memory and the stores-as-collectives of the tensor-parallel layer -----------------------
+// A zero-filled device buffer other processes of the node can map, as a uint8 tensor, and the bytes of
+// its CUDA IPC handle.
+py::tuple peer_alloc(int64_t nbytes) {
+    void* ptr = nullptr;
+    char handle[BSI_B200_PEER_HANDLE_BYTES];
+    check_status(bsi_b200_peer_alloc(nbytes, &ptr, handle), "bsi_b200_peer_alloc");
+    const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
+    at::Tensor t = at::from_blob(ptr, {nbytes}, [](void* p) { bsi_b200_peer_free(p); },
+                                 at::TensorOptions().dtype(at::kByte).device(dev));
+    return py::make_tuple(t, py::bytes(handle, sizeof(handle)));
+}
+
+int64_t peer_open(py::bytes handle) {
+    std::string h = handle;
+    TORCH_CHECK(h.size() == BSI_B200_PEER_HANDLE_BYTES, "peer handle must be ", BSI_B200_PEER_HANDLE_BYTES, " bytes");
+    void* ptr = nullptr;
+    check_status(bsi_b200_peer_open(h.data(), &ptr), "bsi_b200_peer_open");
+    return static_cast<int64_t>(reinterpret_cast<intptr_t>(ptr));
+}
+
+void peer_close(int64_t ptr) { check_status(bsi_b200_peer_close(reinterpret_cast<void*>(static_cast<intptr_t>(ptr))), "bsi_b200_peer_close"); }
+
+void peer_barrier(std::vector<int64_t> flag_ptrs, int rank, int64_t timeout_ms) {
+    std::vector<uint32_t*> f;
+    for (int64_t p : flag_ptrs) f.push_back(reinterpret_cast<uint32_t*>(static_cast<intptr_t>(p)));
+    check_status(bsi_b200_peer_barrier(f.data(), rank, static_cast<int>(f.size()), timeout_ms, current_stream()),
+                 "bsi_b200_peer_barrier");
+}
+
+// pack_queries_into with several destinations given as raw device addresses (own memory or peer
+// mappings): the int8 image lands at q8_ptrs[i] + row * ld8 + col, the chunk scales at
+// scale_ptrs[i] + 4 * (row * scale_ld + chunk).
+void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
+                        int64_t scale_ld, int decimalPlaces) {
+    TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
+    TORCH_CHECK(q8_ptrs.size() == scale_ptrs.size() && !q8_ptrs.empty(), "destination lists must match");
+    check_clip();
+    TORCH_CHECK(chunk_scale_enabled(), "pack_queries_multi needs BSI_FIXED_CHUNK_SCALE=1");
+    at::Tensor x = x2d.detach();
+    if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
+        x = x.to(at::kFloat);
+    if (x.stride(1) != 1) x = x.contiguous();
+    std::vector<int8_t*> q;
+    std::vector<float*> sc;
+    for (size_t i = 0; i < q8_ptrs.size(); ++i) {
+        q.push_back(reinterpret_cast<int8_t*>(static_cast<intptr_t>(q8_ptrs[i])));
+        sc.push_back(reinterpret_cast<float*>(static_cast<intptr_t>(scale_ptrs[i])));
+    }
+    check_status(bsi_b200_quantize_pack_multi(x.data_ptr(), dtype_code(x), x.size(0), x.size(1), x.stride(0), decimalPlaces,
+                                              bits_queries(), static_cast<int>(q.size()), q.data(), ld8, sc.data(),
+                                              scale_ld, current_stream()),
+                 "bsi_b200_quantize_pack_multi");
+}
+
+// linear_from_packed whose rows are dealt out to the matrices at y_ptrs (rows_per_dst rows each, leading
+// dimension ldy, element type out_dtype); returns nothing, the destinations are the caller's buffers.
+void linear_from_packed_scatter(torch::Tensor q8, torch::Tensor scales, py::capsule keyset_cuda_cap,
+                                c10::optional<torch::Tensor> bias, int decimalPlaces, py::object out_dtype, bool relu,
+                                std::vector<int64_t> y_ptrs, int64_t rows_per_dst, int64_t ldy) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
+    TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
+    const int64_t Q = q8.size(0), R = keys->num_keys, chunks = keys->b.chunks;
+    TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
+    TORCH_CHECK(q8.size(1) == chunks * 256, "Word count mismatch between query batch and keys");
+    TORCH_CHECK(scales.numel() == Q * chunks, "scales shape mismatch");
+    TORCH_CHECK(decimalPlaces == keys->b.decimals, "Decimal mismatch between queries and keys");
+    const int total_decimals = decimalPlaces + keys->b.decimals;
+    const double scale_inv = total_decimals > 0 ? 1.0 / std::pow(10.0, total_decimals) : 1.0;
+    const at::ScalarType yt = torch::python::detail::py_object_to_dtype(out_dtype);
+    TORCH_CHECK(yt == at::kFloat || yt == at::kHalf || yt == at::kBFloat16, "out_dtype must be float32, float16 or bfloat16");
+    const float* bptr = nullptr;
+    at::Tensor b32;
+    if (bias.has_value() && bias->defined()) {
+        b32 = bias->to(q8.device(), at::kFloat).contiguous();
+        TORCH_CHECK(b32.numel() == R, "bias length mismatch");
+        bptr = b32.data_ptr<float>();
+    }
+    std::vector<void*> y;
+    for (int64_t p : y_ptrs) y.push_back(reinterpret_cast<void*>(static_cast<intptr_t>(p)));
+    const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
+    check_status(bsi_b200_linear_i8_scatter(q8.data_ptr<int8_t>(), q8.stride(0), scales.data_ptr<float>(), chunks,
+                                            keys->b.q8.data_ptr<int8_t>(), keys->b.q8.size(1),
+                                            keys->b.scales.data_ptr<float>(), bptr, Q, R, chunks,
+                                            static_cast<float>(scale_inv), static_cast<int>(y.size()), y.data(),
+                                            rows_per_dst, ldy, code, relu ? BSI_ACT_RELU : BSI_ACT_NONE, current_stream()),
+                 "bsi_b200_linear_i8_scatter");
+}
+
 py::dict debug_batch(const PackedBatch& b) {
     py::dict d;
     d["words"] = b.words;
@@ -623,6 +775,21 @@ PYBIND11_MODULE(bsi_ops, m) {
     m.def("bsi_linear_forward", &bsi_linear_forward, py::arg("x2d"), py::arg("keyset_cuda_cap"),
           py::arg("bias") = py::none(), py::arg("decimal_places") = 2,
           "pack + dot + cast + bias for one linear layer");
+    m.def("pack_queries_into", &pack_queries_into, py::arg("x2d"), py::arg("q8"), py::arg("scales"),
+          py::arg("decimal_places"), "Pack activations into caller-owned int8 / chunk-scale tensors");
+    m.def("linear_from_packed", &linear_from_packed, py::arg("q8"), py::arg("scales"), py::arg("keyset_cuda_cap"),
+          py::arg("bias"), py::arg("decimal_places"), py::arg("out_dtype"), py::arg("relu") = false,
+          "Dot of packed activations with a key set, cast + bias (+ ReLU) fused");
+    m.def("peer_alloc", &peer_alloc, py::arg("nbytes"), "Zero-filled device buffer other local processes can map: (uint8 tensor, handle bytes)");
+    m.def("peer_open", &peer_open, py::arg("handle"), "Map a peer's buffer; returns its device address here");
+    m.def("peer_close", &peer_close, py::arg("ptr"));
+    m.def("peer_barrier", &peer_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("timeout_ms") = 2000,
+          "Bounded flag barrier over the ranks, enqueued on the current stream");
+    m.def("pack_queries_multi", &pack_queries_multi, py::arg("x2d"), py::arg("q8_ptrs"), py::arg("ld8"),
+          py::arg("scale_ptrs"), py::arg("scale_ld"), py::arg("decimal_places"));
+    m.def("linear_from_packed_scatter", &linear_from_packed_scatter, py::arg("q8"), py::arg("scales"),
+          py::arg("keyset_cuda_cap"), py::arg("bias"), py::arg("decimal_places"), py::arg("out_dtype"), py::arg("relu"),
+          py::arg("y_ptrs"), py::arg("rows_per_dst"), py::arg("ldy"));
     m.def("debug_query_batch_tensors", &debug_query_batch_tensors);
     m.def("debug_keys_tensors", &debug_keys_tensors);
     m.def("debug_query_tensors", &debug_query_tensors);

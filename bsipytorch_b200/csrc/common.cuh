@@ -42,4 +42,14 @@ int sm_count();
 // 0 when the current device is sm_100 class, an error code otherwise.
 int require_sm100();
 
+// Destinations of a linear whose output rows are dealt out to several matrices (n = 0: plain output).
+struct ScatterDst {
+    int n;
+    int rows_per_dst;                 // multiple of 32
+    void* y[BSI_B200_MAX_PEERS];      // row q -> y[q / rows_per_dst], local row q % rows_per_dst
+};
+
+// Reads and clears the status word of the peer barrier kernels (0 = clean, 64 + p = gave up waiting for rank p).
+int take_peer_status(int* v);
+
 }  // namespace bsi

@@ -14,7 +14,8 @@ int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_st
 
 int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride, const int8_t* k8, int64_t ldk,
                 const float* bw0, const float* bias, int64_t Q, int64_t R, int64_t chunks, float scale_inv,
-                void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, cudaStream_t stream);
+                void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, int relu,
+                const ScatterDst* scatter, cudaStream_t stream);
 
 int dot_words_bmma(const uint64_t* A, const float* qs, int64_t qs_stride, int Sa, int64_t W,
                    const uint64_t* B, const float* Bw, int Sb, int64_t R, int64_t Q, float scale_inv,
@@ -144,10 +145,10 @@ extern "C" int bsi_b200_dot_i8(const int8_t* a8, int64_t lda, const float* qs, i
     return fail(BSI_ERR_INVALID, "dot_i8: engine must be AUTO, TCGEN05 or SIMT (BMMA takes slice words: bsi_b200_dot_words)");
 }
 
-extern "C" int bsi_b200_linear_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+extern "C" int bsi_b200_linear_i8_act(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
                                   const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
                                   int64_t Q, int64_t R, int64_t chunks, float scale_inv,
-                                  void* y, int64_t ldy, int y_dtype, bsi_stream_t stream_) {
+                                  void* y, int64_t ldy, int y_dtype, int activation, bsi_stream_t stream_) {
     using namespace bsi;
     if (Q < 0 || R < 0 || chunks < 0) return fail(BSI_ERR_INVALID, "linear_i8: negative size");
     if (Q == 0 || R == 0) return BSI_OK;
@@ -159,11 +160,59 @@ extern "C" int bsi_b200_linear_i8(const int8_t* a8, int64_t lda, const float* qs
         return fail(BSI_ERR_INVALID, "linear_i8: a8/k8 need 16-byte aligned rows of at least 256*chunks bytes");
     if (ldy < R) return fail(BSI_ERR_INVALID, "linear_i8: ldy < R");
     if (qs_stride != 0 && qs_stride < chunks) return fail(BSI_ERR_INVALID, "linear_i8: qs_stride < chunks");
+    if (activation != BSI_ACT_NONE && activation != BSI_ACT_RELU)
+        return fail(BSI_ERR_INVALID, "linear_i8: unknown activation");
     if (y_dtype != BSI_DTYPE_F32 && y_dtype != BSI_DTYPE_F16 && y_dtype != BSI_DTYPE_BF16)
         return fail(BSI_ERR_INVALID, "linear_i8: unknown y_dtype");
     if (int rc = require_sm100()) return rc;
     return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, bias, Q, R, chunks, scale_inv, y, ldy, y_dtype,
-                       nullptr, 0, static_cast<cudaStream_t>(stream_));
+                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, nullptr, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int bsi_b200_linear_i8_scatter(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                                          const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                                          int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                                          int n_dst, void* const* y_dst, int64_t rows_per_dst, int64_t ldy,
+                                          int y_dtype, int activation, bsi_stream_t stream_) {
+    using namespace bsi;
+    if (Q < 0 || R < 0 || chunks < 0) return fail(BSI_ERR_INVALID, "linear_i8_scatter: negative size");
+    if (Q == 0 || R == 0) return BSI_OK;
+    if (a8 == nullptr || k8 == nullptr || qs == nullptr || bw0 == nullptr || y_dst == nullptr)
+        return fail(BSI_ERR_INVALID, "linear_i8_scatter: null pointer");
+    if (chunks == 0) return fail(BSI_ERR_INVALID, "linear_i8_scatter: chunks must be positive");
+    if (lda < chunks * 256 || ldk < chunks * 256 || (lda & 15) || (ldk & 15) ||
+        (reinterpret_cast<uintptr_t>(a8) & 15) || (reinterpret_cast<uintptr_t>(k8) & 15))
+        return fail(BSI_ERR_INVALID, "linear_i8_scatter: a8/k8 need 16-byte aligned rows of at least 256*chunks bytes");
+    if (ldy < R) return fail(BSI_ERR_INVALID, "linear_i8_scatter: ldy < R");
+    if (qs_stride != 0 && qs_stride < chunks) return fail(BSI_ERR_INVALID, "linear_i8_scatter: qs_stride < chunks");
+    if (activation != BSI_ACT_NONE && activation != BSI_ACT_RELU)
+        return fail(BSI_ERR_INVALID, "linear_i8_scatter: unknown activation");
+    if (y_dtype != BSI_DTYPE_F32 && y_dtype != BSI_DTYPE_F16 && y_dtype != BSI_DTYPE_BF16)
+        return fail(BSI_ERR_INVALID, "linear_i8_scatter: unknown y_dtype");
+    if (n_dst < 1 || n_dst > BSI_B200_MAX_PEERS || rows_per_dst <= 0 || rows_per_dst > 0x7fffffe0ll)
+        return fail(BSI_ERR_INVALID, "linear_i8_scatter: bad n_dst / rows_per_dst");
+    ScatterDst sc = {};
+    sc.n = n_dst;
+    sc.rows_per_dst = static_cast<int>(rows_per_dst);
+    // the kernel chooses 16-byte or scalar stores from destination 0: all must be aligned alike
+    const uintptr_t align0 = reinterpret_cast<uintptr_t>(y_dst[0]) & 15;
+    for (int i = 0; i < n_dst; ++i) {
+        if (y_dst[i] == nullptr) return fail(BSI_ERR_INVALID, "linear_i8_scatter: null destination");
+        if ((reinterpret_cast<uintptr_t>(y_dst[i]) & 15) != align0)
+            return fail(BSI_ERR_INVALID, "linear_i8_scatter: destinations must share their 16-byte alignment");
+        sc.y[i] = y_dst[i];
+    }
+    if (int rc = require_sm100()) return rc;
+    return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, bias, Q, R, chunks, scale_inv, nullptr, ldy, y_dtype,
+                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, &sc, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int bsi_b200_linear_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                                  const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                                  int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                                  void* y, int64_t ldy, int y_dtype, bsi_stream_t stream_) {
+    return bsi_b200_linear_i8_act(a8, lda, qs, qs_stride, k8, ldk, bw0, bias, Q, R, chunks, scale_inv, y, ldy, y_dtype,
+                                  BSI_ACT_NONE, stream_);
 }
 
 extern "C" int bsi_b200_dot_words(const uint64_t* A, const float* qs, int64_t qs_stride, int Sa, int64_t W,

@@ -431,7 +431,7 @@ int launch_tile(const CUtensorMap& ma, const CUtensorMap& mb, const float* qs, i
 template <int BN, bool DBG, typename OutT>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
                 const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
-                float scale_inv, void* out, int64_t ldo, int32_t* dbg, cudaStream_t stream) {
+                float scale_inv, void* out, int64_t ldo, int32_t* dbg, const ScatterDst& scatter, cudaStream_t stream) {
     using C = pair::Cfg<BN>;
     static int max_clusters[64] = {0};
     int dev = 0;
@@ -463,7 +463,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     const int pairs = tiles_total < resident ? tiles_total : resident;
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>, ma, mb, vector_store, qs,
-                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg));
+                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter));
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
@@ -512,7 +512,16 @@ int pick_bn(int64_t Q, int64_t R) {
 // Paired-CTA engine with the output type and the bias chosen at run time (y_dtype: BSI_DTYPE_*).
 int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride, const int8_t* k8, int64_t ldk,
                 const float* bw0, const float* bias, int64_t Q, int64_t R, int64_t chunks, float scale_inv,
-                void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, cudaStream_t stream) {
+                void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, int relu,
+                const ScatterDst* scatter_in, cudaStream_t stream) {
+    ScatterDst scatter = {};
+    if (scatter_in != nullptr) {
+        scatter = *scatter_in;
+        if (scatter.n < 1 || scatter.n > BSI_B200_MAX_PEERS || scatter.rows_per_dst <= 0 || (scatter.rows_per_dst & 31) != 0 ||
+            static_cast<int64_t>(scatter.n) * scatter.rows_per_dst < Q)
+            return fail(BSI_ERR_INVALID, "dot_i8: scatter needs 1..16 destinations of a multiple of 32 rows covering Q");
+        out = scatter.y[0];
+    }
     if (Q > 0x7fffff00ll || R > 0x7fffff00ll || chunks > 0x400000)
         return fail(BSI_ERR_UNSUPPORTED, "dot_i8: Q, R or chunks too large");
     const int bn = force_bn ? force_bn : pick_bn_pair(Q, R);
@@ -527,11 +536,12 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     const int esz = y_dtype == BSI_DTYPE_F32 ? 4 : 2;
     const int per16 = 16 / esz;
     const int vector_store =
-        ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo % per16) == 0 && (R % per16) == 0) ? 1 : 0;
+        (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo % per16) == 0 && (R % per16) == 0) ? 1 : 0) |
+        (relu ? 2 : 0);   // the kernel's store_flags
     const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
 #define BSI_PAIR_T(BN_, DBG_, T_)                                                                              \
     launch_pair<BN_, DBG_, T_>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv, out, ldo,  \
-                               dbg_iacc, stream)
+                               dbg_iacc, scatter, stream)
 #define BSI_PAIR(BN_)                                                                   \
     (y_dtype == BSI_DTYPE_F16    ? BSI_PAIR_T(BN_, false, __half)                       \
      : y_dtype == BSI_DTYPE_BF16 ? BSI_PAIR_T(BN_, false, __nv_bfloat16)                \
@@ -555,7 +565,7 @@ int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_st
     const bool want_pair = force_bn ? (force_bn >= 2000) : (Q > 128);
     if (want_pair) {
         return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, nullptr, Q, R, chunks, scale_inv, out, ldo,
-                           BSI_DTYPE_F32, dbg_iacc, force_bn ? force_bn - 2000 : 0, stream);
+                           BSI_DTYPE_F32, dbg_iacc, force_bn ? force_bn - 2000 : 0, /*relu=*/0, nullptr, stream);
     }
     const int bn = force_bn ? force_bn : pick_bn(Q, R);
     CUtensorMap ma, mb;
@@ -588,6 +598,9 @@ extern "C" int bsi_b200_device_status(int* status_out) {
         const int zero = 0;
         BSI_CUDA_TRY(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
     }
+    int pv = 0;
+    if (int rc = take_peer_status(&pv)) return rc;
+    if (v == 0) v = pv;
     *status_out = v;
     return BSI_OK;
 }

@@ -168,13 +168,19 @@ __device__ __forceinline__ __nv_bfloat16 finish<__nv_bfloat16>(float v, float bi
     return has_bias ? __float2bfloat16_rn(__bfloat162float(h) + __bfloat162float(__float2bfloat16_rn(bias))) : h;
 }
 
+// max(v, 0) on the finished output value when the layer's activation is fused (NaN stays NaN).
+template <typename OutT>
+__device__ __forceinline__ OutT relu_if(OutT v, bool relu) {
+    return (relu && static_cast<float>(v) < 0.0f) ? static_cast<OutT>(0.0f) : v;
+}
+
 template <int BN, bool DBG, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-    int vector_store,
+    int store_flags,   // bit 0: 16-byte vector stores are possible; bit 1: ReLU on the finished value
     const float* __restrict__ qs, int64_t qs_stride, const float* __restrict__ bw0,
     const float* __restrict__ bias, int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
-    void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc) {
+    void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc, const ScatterDst scatter) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     constexpr int kCols = BN / 2;       // accumulator columns per epilogue warp
@@ -204,6 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const int num_pairs = gridDim.x >> 1;
     const int num_kb = chunks * 2;
     const bool has_bias = bias != nullptr;
+    const bool relu = (store_flags & 2) != 0;
 
     const uint32_t leader_full0 = map_to_cta(full_bar(0), 0);
     AbortCtx actx;
@@ -396,7 +403,14 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
             constexpr int kRounds = kCols / kRoundCols;
             constexpr int kRowBytes = kChunks * 16;
             OutT* outp = static_cast<OutT*>(out);
-            if (vector_store) {
+            int row_shift = 0;   // first global row of the destination matrix this warp's 32 rows belong to
+            if (scatter.n > 0) {
+                int d = row_base / scatter.rows_per_dst;
+                d = d < scatter.n ? d : scatter.n - 1;
+                outp = static_cast<OutT*>(scatter.y[d]);
+                row_shift = d * scatter.rows_per_dst;
+            }
+            if ((store_flags & 1)) {
 #pragma unroll
                 for (int g = 0; g < kRounds; ++g) {
                     const int colg = n0 + col0 + g * kRoundCols;
@@ -409,7 +423,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                             const int j = g * kRoundCols + ch * kPerChunk + e;
                             const float w = __shfl_sync(0xffffffffu, bwreg[j & 3], j >> 2);
                             const float bv = __shfl_sync(0xffffffffu, biasreg[j & 3], j >> 2);
-                            vals[e] = finish<OutT>((acc[j] * w) * scale_inv, bv, has_bias);
+                            vals[e] = relu_if<OutT>(finish<OutT>((acc[j] * w) * scale_inv, bv, has_bias), relu);
                         }
                         const int swz = kChunks == 8 ? (ch ^ (lane & 7)) : (ch ^ ((lane >> 1) & 3));
                         *reinterpret_cast<uint4*>(dst + (swz << 4)) = *reinterpret_cast<const uint4*>(vals);
@@ -424,19 +438,19 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                         const uint4 o = *reinterpret_cast<const uint4*>(my_store + rr * kRowBytes + (swz << 4));
                         const int grow = row_base + rr;
                         if (grow < Q && col < R) {   // R is a multiple of kPerChunk on this path
-                            *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(grow) * ldo + col) = o;
+                            *reinterpret_cast<uint4*>(outp + static_cast<int64_t>(grow - row_shift) * ldo + col) = o;
                         }
                     }
                     __syncwarp();
                 }
             } else {
-                OutT* orow = outp + static_cast<int64_t>(row_ok ? row : 0) * ldo;
+                OutT* orow = outp + static_cast<int64_t>(row_ok ? row - row_shift : 0) * ldo;
 #pragma unroll
                 for (int j = 0; j < kCols; ++j) {
                     const int col = n0 + col0 + j;
                     const float w = __shfl_sync(0xffffffffu, bwreg[j & 3], j >> 2);
                     const float bv = __shfl_sync(0xffffffffu, biasreg[j & 3], j >> 2);
-                    if (row_ok && col < R) orow[col] = finish<OutT>((acc[j] * w) * scale_inv, bv, has_bias);
+                    if (row_ok && col < R) orow[col] = relu_if<OutT>(finish<OutT>((acc[j] * w) * scale_inv, bv, has_bias), relu);
                 }
             }
         }

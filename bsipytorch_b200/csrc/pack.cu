@@ -257,17 +257,13 @@ __global__ void __launch_bounds__(256) quantize_pack_chunk_generic_kernel(
 //    again: u = fma(r1, 2^-s, 0.5 - 2^(23-s)) is exact and its 2^23-truncation carries the result in the
 //    low mantissa byte. All of this runs on the FMA pipe.
 //  * float32 inputs, 10^dp <= 127: 32-bit integer arithmetic on the float's bit pattern.
-template <typename T, bool kWords, bool kQ8>
-__device__ __forceinline__ bool fast_chunk(const float (&f)[8], uint32_t unit, uint32_t q8_off, uint32_t word_off,
-                                           bool word_ok, int lane, uint32_t dec_mult, int bits, uint32_t slice_bytes,
-                                           u64* __restrict__ words, float* __restrict__ scales,
-                                           int32_t* __restrict__ shifts, int8_t* __restrict__ q8) {
+template <typename T>
+__device__ __forceinline__ bool fast_quantise(const float (&f)[8], uint32_t dec_mult, int bits, int& shift, u64& packed) {
     uint32_t amax_bits = 0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) amax_bits = max(amax_bits, __float_as_uint(f[e]) & 0x7fffffffu);
     amax_bits = __reduce_max_sync(0xffffffffu, amax_bits);   // NaN and inf order above every finite value
 
-    int shift;
     uint32_t u[8];
     if constexpr (sizeof(T) == 2) {
         const float fmult = static_cast<float>(dec_mult);
@@ -293,11 +289,23 @@ __device__ __forceinline__ bool fast_chunk(const float (&f)[8], uint32_t unit, u
         for (int e = 0; e < 8; ++e)
             u[e] = (decimal_round_mag32(__float_as_uint(f[e]), dec_mult) + round_add) >> shift;
     }
+    packed = sign_clamp_bytes(u, f, bits);
+    return true;
+}
+
+// Fast path of one chunk including its stores: true when the chunk was quantised and stored.
+template <typename T, bool kWords, bool kQ8>
+__device__ __forceinline__ bool fast_chunk(const float (&f)[8], uint32_t unit, uint32_t q8_off, uint32_t word_off,
+                                           bool word_ok, int lane, uint32_t dec_mult, int bits, uint32_t slice_bytes,
+                                           u64* __restrict__ words, float* __restrict__ scales,
+                                           int32_t* __restrict__ shifts, int8_t* __restrict__ q8) {
+    int shift;
+    u64 packed;
+    if (!fast_quantise<T>(f, dec_mult, bits, shift, packed)) return false;
     if (lane == 0) {
         scales[unit] = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);   // 2^shift
         if (shifts != nullptr) shifts[unit] = shift;
     }
-    const u64 packed = sign_clamp_bytes(u, f, bits);
     if constexpr (kQ8) *reinterpret_cast<u64*>(q8 + q8_off) = packed;
     if constexpr (kWords) {
         if (word_ok) {
@@ -437,6 +445,109 @@ __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_chunk_
         for (uint32_t unit = first; unit < g.total; unit += stride)
             generic_unit<T>(x, unit, g.D, g.ldx, dec_scale, dec_mult, bits, g.chunks, g.W, words, scales, shifts, q8,
                             ld8, vec, lane);
+    }
+}
+
+// Destinations of the multi-destination pack: the same int8 image / chunk scales go to each of them.
+struct MultiDst {
+    int n;
+    int8_t* q8[BSI_B200_MAX_PEERS];
+    float* scales[BSI_B200_MAX_PEERS];
+};
+
+// Generic quantiser of one chunk without the stores (the multi-destination kernel's fallback).
+__device__ __noinline__ void generic_quantise(float f0, float f1, float f2, float f3, float f4, float f5, float f6,
+                                              float f7, double dec_scale, uint32_t dec_mult, int bits, int* shift_out,
+                                              u64* packed_out) {
+    const float f[8] = {f0, f1, f2, f3, f4, f5, f6, f7};
+    long long v[8];
+    u64 mx = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        v[e] = decimal_round(f[e], dec_scale, dec_mult);
+        const u64 a = uabs(v[e]);
+        mx = a > mx ? a : mx;
+    }
+    mx = warp_max_u64(mx);
+    const int shift = shift_for(mx, bits);
+    const long long qmax = (1ll << (bits - 1)) - 1ll;
+    const long long qmin = -(1ll << (bits - 1));
+    const u64 round_add = shift > 0 ? (1ull << (shift - 1)) : 0ull;
+    u64 packed = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const u64 uq = (uabs(v[e]) + round_add) >> shift;
+        long long q = v[e] < 0 ? -static_cast<long long>(uq) : static_cast<long long>(uq);
+        q = q < qmin ? qmin : q;
+        q = q > qmax ? qmax : q;
+        packed |= (static_cast<u64>(q) & 0xffull) << (8 * e);
+    }
+    *shift_out = shift;
+    *packed_out = packed;
+}
+
+// Chunk-mode pack whose int8 image and chunk scales are stored to several destinations at once (own
+// memory and peer mappings alike): element (row, col) at q8[i] + row * ld8 + col, the scale of
+// (row, chunk) at scales[i] + row * scale_ld + chunk. Persistent warps with next-unit prefetch as in
+// the fast kernel; D is a multiple of 256 and x is 16-byte aligned, so every lane loads vectors.
+template <typename T>
+__global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_multi_kernel(
+    const T* __restrict__ x, uint32_t total, uint32_t chunks, uint32_t ldx, uint32_t ld8, uint32_t scale_ld,
+    double dec_scale, uint32_t dec_mult, uint32_t fast_limit, int bits, const MultiDst dst) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t stride = gridDim.x * 8u;
+    const uint32_t first = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (first >= total) return;
+    const uint32_t stride_rows = stride / chunks;
+    const uint32_t stride_chunks = stride - stride_rows * chunks;
+    const uint32_t lane_col = lane * 8u;
+    const bool try_fast = dec_mult != 0u && dec_mult <= fast_limit;
+
+    struct Pos { uint32_t unit, row, chunk; };
+    auto advance = [&](Pos p) {
+        p.unit += stride; p.row += stride_rows; p.chunk += stride_chunks;
+        if (p.chunk >= chunks) { p.chunk -= chunks; ++p.row; }
+        return p;
+    };
+    auto fetch = [&](RawLane<T>& r, const Pos& p) { r.load(x + (p.row * ldx + p.chunk * 256u + lane_col)); };
+    auto process = [&](const RawLane<T>& r, const Pos& p) {
+        float f[8];
+        r.to_floats(f);
+        int shift;
+        u64 packed;
+        if (!(try_fast && fast_quantise<T>(f, dec_mult, bits, shift, packed)))
+            generic_quantise(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], dec_scale, dec_mult, bits, &shift, &packed);
+        const uint32_t q8_off = p.row * ld8 + p.chunk * 256u + lane_col;
+        const uint32_t sc_off = p.row * scale_ld + p.chunk;
+        const float scale = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);   // 2^shift, shift <= 62
+#pragma unroll
+        for (int i = 0; i < BSI_B200_MAX_PEERS; ++i) {
+            if (i < dst.n) {
+                *reinterpret_cast<u64*>(dst.q8[i] + q8_off) = packed;
+                if (lane == 0) dst.scales[i][sc_off] = scale;
+            }
+        }
+    };
+
+    Pos cur;
+    cur.unit = first;
+    cur.row = first / chunks;
+    cur.chunk = first - cur.row * chunks;
+    RawLane<T> a, b;
+    fetch(a, cur);
+    for (;;) {
+        Pos nxt = advance(cur);
+        bool more = nxt.unit < total;
+        if (more) fetch(b, nxt);
+        process(a, cur);
+        if (!more) break;
+        cur = nxt;
+        nxt = advance(cur);
+        more = nxt.unit < total;
+        if (more) fetch(a, nxt);
+        process(b, cur);
+        if (!more) break;
+        cur = nxt;
     }
 }
 
@@ -682,6 +793,62 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
 #undef BSI_LAUNCH_ROW
     }
     return check_launch("quantize_pack launch");
+}
+
+extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                                            int decimal_places, int bits, int n_dst, int8_t* const* q8_dst,
+                                            int64_t ld8, float* const* scale_dst, int64_t scale_ld,
+                                            bsi_stream_t stream_) {
+    using namespace bsi;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (rows < 0 || D < 0 || ldx < D) return fail(BSI_ERR_INVALID, "quantize_pack_multi: bad rows/D/ldx");
+    if (bits < 2 || bits > 8) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack_multi: bits must be in [2, 8]");
+    if (dtype != BSI_DTYPE_F32 && dtype != BSI_DTYPE_F16 && dtype != BSI_DTYPE_BF16)
+        return fail(BSI_ERR_INVALID, "quantize_pack_multi: unknown dtype");
+    if (n_dst < 1 || n_dst > BSI_B200_MAX_PEERS || q8_dst == nullptr || scale_dst == nullptr)
+        return fail(BSI_ERR_INVALID, "quantize_pack_multi: bad destinations");
+    if (rows == 0 || D == 0) return BSI_OK;
+    if (x == nullptr) return fail(BSI_ERR_INVALID, "quantize_pack_multi: x is null");
+    if ((D & 255) != 0) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack_multi: D must be a multiple of 256");
+    const int64_t chunks = D / 256;
+    const int esz = dtype == BSI_DTYPE_F32 ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((ldx * esz) & 15) != 0)
+        return fail(BSI_ERR_INVALID, "quantize_pack_multi: x needs 16-byte aligned rows");
+    if (ld8 < D || (ld8 & 7) != 0 || scale_ld < chunks)
+        return fail(BSI_ERR_INVALID, "quantize_pack_multi: ld8 >= D, ld8 % 8 == 0 and scale_ld >= D/256 are required");
+    int64_t widest = ldx > ld8 ? ldx : ld8;
+    if (rows * widest >= (1ll << 31)) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack_multi: matrix too large for one launch");
+    MultiDst dst = {};
+    dst.n = n_dst;
+    for (int i = 0; i < n_dst; ++i) {
+        if (q8_dst[i] == nullptr || scale_dst[i] == nullptr || (reinterpret_cast<uintptr_t>(q8_dst[i]) & 7) != 0)
+            return fail(BSI_ERR_INVALID, "quantize_pack_multi: destinations must be non-null, q8 8-byte aligned");
+        dst.q8[i] = q8_dst[i];
+        dst.scales[i] = scale_dst[i];
+    }
+    if (int rc = require_sm100()) return rc;
+    const double dec_scale = pow(10.0, static_cast<double>(decimal_places));
+    uint32_t dec_mult = 0;
+    if (decimal_places >= 0 && decimal_places <= 8) {
+        dec_mult = 1;
+        for (int i = 0; i < decimal_places; ++i) dec_mult *= 10u;
+    }
+#define BSI_LAUNCH_MULTI(T, LIMIT)                                                                          \
+    do {                                                                                                    \
+        const int64_t resident = resident_blocks(quantize_pack_multi_kernel<T>);                            \
+        if (resident <= 0) return BSI_ERR_CUDA;                                                             \
+        int64_t blocks = (rows * chunks + 7) / 8;                                                           \
+        blocks = blocks < resident ? blocks : resident;                                                     \
+        quantize_pack_multi_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                   \
+            static_cast<const T*>(x), static_cast<uint32_t>(rows * chunks), static_cast<uint32_t>(chunks),  \
+            static_cast<uint32_t>(ldx), static_cast<uint32_t>(ld8), static_cast<uint32_t>(scale_ld), dec_scale, \
+            dec_mult, LIMIT, bits, dst);                                                                    \
+    } while (0)
+    if (dtype == BSI_DTYPE_F32) BSI_LAUNCH_MULTI(float, 127u);
+    else if (dtype == BSI_DTYPE_F16) BSI_LAUNCH_MULTI(__half, 1000u);
+    else BSI_LAUNCH_MULTI(__nv_bfloat16, 1000u);
+#undef BSI_LAUNCH_MULTI
+    return check_launch("quantize_pack_multi launch");
 }
 
 extern "C" int bsi_b200_recombine_i8(const uint64_t* words, int64_t rows, int bits, int64_t W,

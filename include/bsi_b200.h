@@ -115,6 +115,62 @@ int bsi_b200_linear_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t q
                        int64_t Q, int64_t R, int64_t chunks, float scale_inv,
                        void* y, int64_t ldy, int y_dtype, bsi_stream_t stream);
 
+/* bsi_b200_linear_i8 with the layer's activation applied to the finished (cast + bias) value before
+ * it is stored: BSI_ACT_RELU gives max(y, 0) in y's type, what `F.relu(fc1(x))` of the OPT decoder
+ * layer computes (the reference leaves the activation to a separate torch kernel). */
+#define BSI_ACT_NONE 0
+#define BSI_ACT_RELU 1
+int bsi_b200_linear_i8_act(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                           const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                           int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                           void* y, int64_t ldy, int y_dtype, int activation, bsi_stream_t stream);
+
+/* ---- tensor-parallel layer: peer memory on one node, one process per GPU -----------------------
+ * The reference has no multi-GPU code. These calls carry the exchange of a layer whose BSI linears
+ * are sharded along R over the GPUs of one node: packed activations and linear outputs are stored
+ * straight into the buffers of the ranks that consume them, over NVLink, with plain stores. */
+#define BSI_B200_MAX_PEERS 16
+#define BSI_B200_PEER_HANDLE_BYTES 64
+
+/* cudaMalloc'ed, zero-filled buffer other processes of this node can map; handle64 receives the
+ * BSI_B200_PEER_HANDLE_BYTES bytes to send them (CUDA IPC). Free with bsi_b200_peer_free. */
+int bsi_b200_peer_alloc(int64_t bytes, void** dev_ptr, void* handle64);
+int bsi_b200_peer_free(void* dev_ptr);
+/* Maps a buffer another process exported (peer access is enabled on first use); close before the
+ * owner frees it. */
+int bsi_b200_peer_open(const void* handle64, void** peer_ptr);
+int bsi_b200_peer_close(void* peer_ptr);
+
+/* Barrier over the n ranks, enqueued on `stream`: flags[r] points at rank r's array of n + 1 uint32
+ * (in a peer buffer, zero at start; flags[rank] is the caller's own). Slot n of a rank's own array
+ * counts the barriers it has passed, so the launch carries no epoch argument and can be replayed from
+ * a captured graph; every rank must run the same sequence of barriers. The kernel first publishes
+ * everything this GPU wrote before it on the stream, stores its new count into slot `rank` of every
+ * rank's array, then waits until every slot of its own array has reached that count (the comparison
+ * survives wrap-around). A wait that exceeds timeout_ms gives up and sets the device status to
+ * 64 + the missing rank (bsi_b200_device_status), so a lost rank cannot hang the GPU. */
+int bsi_b200_peer_barrier(uint32_t* const* flags, int rank, int n, int64_t timeout_ms, bsi_stream_t stream);
+
+/* Chunk-mode quantise + pack of activations (int8 image and chunk scales only) written to n_dst
+ * places at once: q8_dst[i] + row * ld8 + col, scale_dst[i] + row * scale_ld + chunk. The pointers
+ * already include the column / row offset of this rank's block inside each destination matrix; they
+ * may be peer mappings. D must be a multiple of 256, x 16-byte aligned with ldx * sizeof(x) % 16 == 0. */
+int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                                 int decimal_places, int bits, int n_dst, int8_t* const* q8_dst,
+                                 int64_t ld8, float* const* scale_dst, int64_t scale_ld,
+                                 bsi_stream_t stream);
+
+/* bsi_b200_linear_i8_act whose output rows are dealt out to n_dst matrices: row q goes to
+ * y_dst[q / rows_per_dst] at local row q % rows_per_dst, column r, leading dimension ldy (the
+ * pointers already include this rank's column offset; they may be peer mappings).
+ * rows_per_dst must be a multiple of 32 and n_dst * rows_per_dst >= Q. This is the all-to-all that
+ * turns the [Q, R/G] output block of a rank back into token shards, done by the epilogue's stores. */
+int bsi_b200_linear_i8_scatter(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                               const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                               int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                               int n_dst, void* const* y_dst, int64_t rows_per_dst, int64_t ldy,
+                               int y_dtype, int activation, bsi_stream_t stream);
+
 /* Same result computed from the slice words with mma.sync b1 AND+POPC, argument order of the
  * reference launcher (bsi_cuda_kernels_dot.cuh:2616-2635) minus the tile hints and index
  * arrays. Bw is [R, Sb]; only Bw[r][0] = 2^shift_r enters (the slice weights are +-2^j * Bw[r][0],

@@ -14,10 +14,14 @@ import sys
 
 import numpy as np
 
+import importlib.util
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
-if _HERE not in sys.path:
-    sys.path.insert(0, _HERE)
-import build as _build  # noqa: E402  (oracle/build.py)
+# oracle/build.py, loaded by path: the checker's folder stays off sys.path (a top-level `build` or
+# `oracle` module there would shadow other packages in child processes)
+_spec = importlib.util.spec_from_file_location("bsi_oracle_build", os.path.join(_HERE, "build.py"))
+_build = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(_build)
 
 _lib = None
 

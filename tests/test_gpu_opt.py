@@ -67,3 +67,49 @@ def test_opt125m_forward_batch8_seq128(dtype):
                     m.fused = True
             lb = model(ids)[:, -1]
         assert float((lb - ld).norm() / ld.norm()) < 0.6
+
+
+def test_tensor_parallel_forward_on_one_rank_equals_the_per_linear_model():
+    """World size 1 of the tensor-parallel decoder (fused QKV key set, ReLU inside the fc1 epilogue,
+    activations packed once per consumer) gives the logits of the BSIQuantizedLinear-per-layer model."""
+    from bsipytorch_b200.opt_tp import build_opt_tp
+
+    cfg = opt.OPTConfig(vocab_size=512, hidden_size=512, num_hidden_layers=2, num_attention_heads=8, ffn_dim=2048,
+                        max_position_embeddings=128, name="tiny")
+    ids = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(2)).to(DEV)
+    for dtype in (torch.float16, torch.float32):
+        ref = opt.build_opt_bsi(cfg, dtype=dtype, device=DEV, seed=11)
+        tp = build_opt_tp(cfg, dtype=dtype, device=DEV, seed=11)
+        with torch.no_grad():
+            want, got = ref(ids), tp(ids)
+        assert torch.isfinite(got).all()
+        assert torch.equal(got, want)
+        assert torch.equal(tp.next_token(ids), ref.next_token(ids))
+        tp.capture(4, 32)                                   # replayed from a CUDA graph: same values
+        assert torch.equal(tp(ids), want)
+        ids2 = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(9)).to(DEV)
+        assert torch.equal(tp(ids2), ref(ids2))
+
+
+def test_linear_from_packed_relu_and_column_block_pack():
+    """pack_queries_into writes a column block of a wider int8 matrix; linear_from_packed with relu=True
+    equals relu of the plain call."""
+    from bsipytorch_b200 import bsi_ops
+
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(96, 1024, generator=g).half().to(DEV)
+    w = (torch.randn(320, 1024, generator=g) * 0.02).to(DEV)
+    cap = bsi_ops.build_bsi_keys_cuda(w, 2, 0.5)[0]
+    q8 = torch.zeros(96, 1024, dtype=torch.int8, device=DEV)
+    sc = torch.zeros(96, 4, dtype=torch.float32, device=DEV)
+    for c in range(2):   # two 512-wide feature blocks packed separately, as two ranks would
+        blk_sc = torch.empty(96, 2, dtype=torch.float32, device=DEV)
+        bsi_ops.pack_queries_into(x[:, c * 512:(c + 1) * 512], q8[:, c * 512:(c + 1) * 512], blk_sc, 2)
+        sc[:, c * 2:(c + 1) * 2] = blk_sc
+    bias = torch.randn(320, generator=g).to(DEV)
+    y = bsi_ops.linear_from_packed(q8, sc, cap, bias, 2, torch.float16, False)
+    want = bsi_ops.bsi_linear_forward(x, cap, bias, 2)
+    assert torch.equal(y, want)
+    yr = bsi_ops.linear_from_packed(q8, sc, cap, bias, 2, torch.float16, True)
+    assert torch.equal(yr, torch.relu(want))
+    assert (want < 0).any()
