@@ -34,7 +34,8 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one dot launch, from the ncu capture summarised
 # under profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"fc1": None, "fc2": None}
+NCU_TRAFFIC_BYTES = {"fc1": 17945344, "fc2": None, "pack": 134321152 + 85714944, "pack-lean": 134263552 + 39758592,
+                     "ewah": 58739712 + 235520 + 59304960 + 7084544}
 
 
 def make_inputs(wl, seed=123):
@@ -217,6 +218,133 @@ def time_reference_gpu_kernels(wl):
         return {"unavailable": str(e)[:200]}
 
 
+HBM_WORKLOADS = {
+    "pack": dict(rows=4096, D=16384, lean=False,
+                 name="quantise + bit-slice pack of fp16 activations [4096, 16384] (relu of N(0,1)): 7 slices + int8 image + chunk scales, dp=2"),
+    "pack-lean": dict(rows=4096, D=16384, lean=True,
+                      name="quantise + pack of fp16 activations [4096, 16384] (relu of N(0,1)): int8 image + chunk scales only (the fused layer path), dp=2"),
+    "ewah": dict(rows=4096, D=16384, lean=False,
+                 name="EWAH/verbatim encode (flags, sizes, offsets, emit) of the 28672 slices x 256 words of packed relu activations [4096, 16384], threshold 0.5"),
+}
+
+
+def run_hbm(args, rank, world, local_rank):
+    """The HBM-bound kernels of the path, each as its own workload: GB/s of algorithmic bytes against the
+    measured copy bandwidth. Inputs rotate over sets larger than L2; N > 1 runs independent replicas."""
+    import ctypes as C
+
+    import torch
+
+    from bsipytorch_b200 import capi
+    spec = HBM_WORKLOADS[args.workload]
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    rows, D = spec["rows"], spec["D"]
+    W, chunks, bits = D // 64, D // 256, 7
+    L = capi.lib()
+    g = torch.Generator().manual_seed(5)
+    nsets = 3
+    xs = [torch.relu(torch.randn(rows, D, generator=g)).to(torch.float16).to(dev) for _ in range(nsets)]
+    words = [torch.empty(rows, bits, W, dtype=torch.int64, device=dev) for _ in range(nsets)]
+    q8 = torch.empty(rows, D, dtype=torch.int8, device=dev)
+    sc = torch.empty(rows, chunks, dtype=torch.float32, device=dev)
+    stream = capi.stream_ptr()
+
+    def pack(i, lean):
+        capi.check(L.bsi_b200_quantize_pack(capi.ptr(xs[i]), 1, rows, D, D, 2, bits, 1, None if lean else capi.ptr(words[i]),
+                                            capi.ptr(sc), None, capi.ptr(q8), D, stream), "quantize_pack")
+
+    if args.workload == "ewah":
+        for i in range(nsets):
+            pack(i, False)
+        S = rows * bits
+        scratch = torch.empty(max(int(L.bsi_b200_ewah_scratch_bytes(S)), 8), dtype=torch.uint8, device=dev)
+        cap = S * (W + 1)
+        out = torch.empty(cap, dtype=torch.int64, device=dev)
+        off = torch.empty(S, dtype=torch.int64, device=dev)
+        length = torch.empty(S, dtype=torch.int32, device=dev)
+        flags = torch.empty(S, dtype=torch.int32, device=dev)
+        total = torch.zeros(1, dtype=torch.int64, device=dev)
+
+        def step(i):
+            capi.check(L.bsi_b200_ewah_encode(capi.ptr(words[i % nsets]), S, W, C.c_double(0.5), capi.ptr(scratch), scratch.numel(),
+                                              capi.ptr(out), cap, capi.ptr(off), capi.ptr(length), capi.ptr(flags),
+                                              capi.ptr(total), stream), "ewah_encode")
+        step(0)
+        torch.cuda.synchronize()
+        stream_words = int(total.item())
+        # flags pass reads the words once, the size pass the compressible slices again, emit reads all and writes the stream
+        bytes_step = 2 * S * W * 8 + stream_words * 8 + S * 24
+        launches, kernel = 4, "ewah_flags_kernel + ewah_size_kernel + ewah_offsets_kernel + ewah_emit_kernel"
+        extra = {"stream_words": stream_words, "input_words": S * W}
+    else:
+        lean = spec["lean"]
+
+        def step(i):
+            pack(i % nsets, lean)
+        bytes_step = rows * D * 2 + rows * D + rows * chunks * 4 + (0 if lean else rows * bits * W * 8)
+        launches, kernel = 1, "quantize_pack_chunk_fast_kernel<__half>"
+        extra = {}
+    warmup, K = max(3, args.warmup), args.steps
+    for i in range(warmup):
+        step(i)
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record()
+    for i in range(K):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.stop()
+    ms = e0.elapsed_time(e1)
+    # end to end through the public module, from pinned host activations (pack only)
+    e2e = None
+    if args.workload != "ewah":
+        import bsipytorch_b200
+        host = xs[0].cpu().pin_memory()
+        n = max(3, min(10, args.e2e_steps))
+        back = torch.empty(rows, chunks, dtype=torch.float32).pin_memory()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n):
+            cap_q = bsipytorch_b200.bsi_ops.build_bsi_queries_cuda_batch_packed(host.to(dev, non_blocking=True), 2, 0.5)
+            back.copy_(bsipytorch_b200.bsi_ops.debug_query_batch_tensors(cap_q)["scales"], non_blocking=True)
+        t1.record()
+        torch.cuda.synchronize()
+        e2e_ms = t0.elapsed_time(t1) / n
+        e2e = {"value": bytes_step / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": rows * D * 2,
+               "d2h_bytes_per_step": rows * chunks * 4, "ms_per_step": e2e_ms, "steps": n,
+               "path": "pinned host fp16 -> H2D -> build_bsi_queries_cuda_batch_packed -> D2H chunk scales"}
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        peaks = measured_peaks()
+        gbs = bytes_step * K / (ms * 1e-3) / 1e9
+        line = {"metric": "BSI " + args.workload + " GB/s", "value": gbs * world, "unit": "GB/s", "n_gpus": world, "steps": K,
+                "warmup": warmup, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "fp16 -> int64 fixed point -> 7-bit slices / int8" if args.workload != "ewah" else "u64",
+                "data": "synthetic",
+                "config": {"workload": spec["name"], "l2": f"{nsets} rotating input sets of {rows * D * 2 >> 20} MiB (> 126 MiB L2 in total)",
+                           "parallelism": "independent replicas" if world > 1 else "1 GPU", **extra},
+                "e2e": e2e, "gpu_launches": K * launches, "clocks": sampler.summary(),
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth",
+                             "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "kernel": kernel,
+                             "algorithmic_bytes_per_step": bytes_step}}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 OPT_WORKLOADS = {
     "opt-125m": dict(batch=8, seq=128, dtype="float16"),
     "opt-6.7b": dict(batch=16, seq=256, dtype="float16"),
@@ -246,7 +374,7 @@ def run_opt(args, rank, world, local_rank):
         # fused QKV key set, head-sharded attention, token-sharded residual stream, packed int8 exchanges
         from bsipytorch_b200.opt_tp import build_opt_tp
         model = build_opt_tp(args.workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world,
-                             exchange=args.exchange)
+                             exchange=args.exchange, push=args.push, microbatches=args.microbatches)
         graphed = bool(args.cuda_graph) and (world == 1 or model.exchange == "peer")
         if graphed:
             model.capture(spec["batch"], spec["seq"])
@@ -314,6 +442,8 @@ def run_opt(args, rank, world, local_rank):
             "config": {"workload": f"{args.workload} random init, batch {B} x seq {T} uniform random ids, all q/k/v/out/fc1/fc2 as BSI ops, dp=2, fixed76 chunkscale",
                        "parallelism": f"{scheme} x{world}" if world > 1 else "1 GPU",
                        "model_impl": args.opt_impl, "launch": "CUDA graph of the decoder stack" if graphed else "eager",
+                       "push": args.push if (world > 1 and args.opt_impl == "tp") else None,
+                       "microbatches": args.microbatches if (world > 1 and args.opt_impl == "tp") else 1,
                        "l2": "weights and activations of one forward exceed the 126 MiB L2" if args.workload != "opt-125m" else "keys of one forward (~150 MB with slices) are about the size of L2"},
             "e2e": {"value": B * T * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8,
                     "d2h_bytes_per_step": B * 8, "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
@@ -339,9 +469,12 @@ def main():
     ap.add_argument("--opt-impl", default="tp", choices=["tp", "layers"],
                     help="OPT workloads: tensor-parallel decoder (default) or one BSIQuantizedLinear per nn.Linear")
     ap.add_argument("--cuda-graph", type=int, default=1, help="tensor-parallel OPT: replay the decoder stack from a CUDA graph")
+    ap.add_argument("--push", default="store", choices=["copy", "store"],
+                    help="peer exchange: int8 blocks pushed by copy engines, or stored to every rank by the pack kernel")
+    ap.add_argument("--microbatches", type=int, default=2, help="peer exchange: sequence groups run on streams of their own")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "collective"],
                     help="tensor-parallel OPT: peer-memory stores (default on GPUs) or NCCL collectives")
-    ap.add_argument("--workload", default="fc1", choices=sorted(WORKLOADS) + sorted(OPT_WORKLOADS))
+    ap.add_argument("--workload", default="fc1", choices=sorted(WORKLOADS) + sorted(OPT_WORKLOADS) + sorted(HBM_WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=30)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
@@ -351,6 +484,15 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    if args.workload in HBM_WORKLOADS:
+        if args.impl == "reference":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the reference's CPU path builds its vectors inside bsiCPP (not vendored); the dot workloads (fc1/fc2) carry the reference arm"}))
+            return
+        if args.steps == 4000:
+            args.steps = 2000
+        run_hbm(args, rank, world, local_rank)
+        return
     if args.workload in OPT_WORKLOADS:
         if args.impl == "reference":
             if rank == 0:
@@ -403,9 +545,21 @@ def main():
     if engine is None and args.engine.startswith("tcgen05:"):
         engine = 1000 + int(args.engine.split(":")[1])
     scale_inv = C.c_float(float(1.0 / 10.0 ** 4))
+    if args.engine == "bmma":      # b1 mma.sync engine: reads the slice words, not the int8 image
+        for s_ in sets:
+            s_["aw"], s_["kw"] = qt["words"].clone(), kt["words"].clone()
+            s_["Bw"] = kt["slice_weights"].clone()
+    elif engine is None:
+        raise SystemExit("unknown --engine " + args.engine)
 
     def step(i):
         s = sets[i % nsets]
+        if args.engine == "bmma":
+            rc = L.bsi_b200_dot_words(capi.ptr(s["aw"]), capi.ptr(s["qs"]), chunks, 7, D // 64, capi.ptr(s["kw"]),
+                                      capi.ptr(s["Bw"]), 6, R, Q, scale_inv, R, capi.ptr(s["out"]), None, capi.stream_ptr())
+            if rc != 0:
+                capi.check(rc, "bsi_b200_dot_words")
+            return
         rc = L.bsi_b200_dot_i8(capi.ptr(s["a8"]), s["a8"].shape[1], capi.ptr(s["qs"]), chunks, capi.ptr(s["k8"]),
                                s["k8"].shape[1], capi.ptr(s["bw0"]), Q, R, chunks, scale_inv, capi.ptr(s["out"]),
                                R, None, engine, capi.stream_ptr())
@@ -508,7 +662,8 @@ def main():
             "roofline": {"bound": "tensor", "achieved": per_gpu_tops, "peak": int8_peak, "unit": "TFLOP/s",
                          "frac": per_gpu_tops / int8_peak,
                          "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16']} (dense int8 = 2 x bf16 on this part)",
-                         "traffic": NCU_TRAFFIC_BYTES[args.workload], "kernel": "dot_i8_tcgen05_kernel",
+                         "traffic": NCU_TRAFFIC_BYTES[args.workload] if args.engine == "tcgen05" else None,
+                         "kernel": {"tcgen05": "dot_i8_tcgen05_pair_kernel", "bmma": "dot_words_bmma_kernel", "simt": "dot_i8_simt_kernel"}.get(args.engine, "dot_i8_tcgen05_pair_kernel"),
                          "algorithmic_ops_per_launch": 2.0 * Q * R * D, "algorithmic_bytes_per_launch": alg_bytes,
                          "hbm_frac_of_measured": (alg_bytes / (ms / K * 1e-3) / 1e9) / peaks["hbm_gbs"]},
             "device_status": status,

@@ -630,7 +630,7 @@ void peer_barrier(std::vector<int64_t> flag_ptrs, int rank, int64_t timeout_ms) 
 void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
                         int64_t scale_ld, int decimalPlaces) {
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
-    TORCH_CHECK(q8_ptrs.size() == scale_ptrs.size() && !q8_ptrs.empty(), "destination lists must match");
+    TORCH_CHECK(!q8_ptrs.empty() && !scale_ptrs.empty(), "destination lists must not be empty");
     check_clip();
     TORCH_CHECK(chunk_scale_enabled(), "pack_queries_multi needs BSI_FIXED_CHUNK_SCALE=1");
     at::Tensor x = x2d.detach();
@@ -639,14 +639,20 @@ void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t
     if (x.stride(1) != 1) x = x.contiguous();
     std::vector<int8_t*> q;
     std::vector<float*> sc;
-    for (size_t i = 0; i < q8_ptrs.size(); ++i) {
-        q.push_back(reinterpret_cast<int8_t*>(static_cast<intptr_t>(q8_ptrs[i])));
-        sc.push_back(reinterpret_cast<float*>(static_cast<intptr_t>(scale_ptrs[i])));
-    }
+    for (int64_t p : q8_ptrs) q.push_back(reinterpret_cast<int8_t*>(static_cast<intptr_t>(p)));
+    for (int64_t p : scale_ptrs) sc.push_back(reinterpret_cast<float*>(static_cast<intptr_t>(p)));
     check_status(bsi_b200_quantize_pack_multi(x.data_ptr(), dtype_code(x), x.size(0), x.size(1), x.stride(0), decimalPlaces,
-                                              bits_queries(), static_cast<int>(q.size()), q.data(), ld8, sc.data(),
-                                              scale_ld, current_stream()),
+                                              bits_queries(), static_cast<int>(q.size()), q.data(), ld8,
+                                              static_cast<int>(sc.size()), sc.data(), scale_ld, current_stream()),
                  "bsi_b200_quantize_pack_multi");
+}
+
+// Copy-engine push of a [height, width_bytes] block between device addresses (own or peer mappings).
+void peer_copy_2d(int64_t dst, int64_t dst_pitch, int64_t src, int64_t src_pitch, int64_t width_bytes, int64_t height) {
+    check_status(bsi_b200_peer_copy_2d(reinterpret_cast<void*>(static_cast<intptr_t>(dst)), dst_pitch,
+                                       reinterpret_cast<const void*>(static_cast<intptr_t>(src)), src_pitch, width_bytes,
+                                       height, current_stream()),
+                 "bsi_b200_peer_copy_2d");
 }
 
 // linear_from_packed whose rows are dealt out to the matrices at y_ptrs (rows_per_dst rows each, leading
@@ -785,6 +791,10 @@ PYBIND11_MODULE(bsi_ops, m) {
     m.def("peer_close", &peer_close, py::arg("ptr"));
     m.def("peer_barrier", &peer_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("timeout_ms") = 2000,
           "Bounded flag barrier over the ranks, enqueued on the current stream");
+    m.def("set_grid_caps", [](int dot_sms, int pack_blocks) { check_status(bsi_b200_set_grid_caps(dot_sms, pack_blocks), "bsi_b200_set_grid_caps"); },
+          py::arg("dot_sms"), py::arg("pack_blocks"), "Cap the SMs of the dot kernels / blocks of the pack kernels (0 = no cap)");
+    m.def("peer_copy_2d", &peer_copy_2d, py::arg("dst"), py::arg("dst_pitch"), py::arg("src"), py::arg("src_pitch"),
+          py::arg("width_bytes"), py::arg("height"));
     m.def("pack_queries_multi", &pack_queries_multi, py::arg("x2d"), py::arg("q8_ptrs"), py::arg("ld8"),
           py::arg("scale_ptrs"), py::arg("scale_ld"), py::arg("decimal_places"));
     m.def("linear_from_packed_scatter", &linear_from_packed_scatter, py::arg("q8"), py::arg("scales"),

@@ -176,20 +176,31 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_kernel(
     if (lane == 0) out_len[s] = static_cast<int32_t>(n);
 }
 
-// Exclusive prefix sum with one block; S is at most a few hundred thousand slices.
+// Exclusive prefix sum with one block; S is at most a few hundred thousand slices. Every thread owns
+// kScanItems consecutive sizes per tile (all of its loads are in flight together, and the next tile's are
+// issued before the current tile is scanned), so a tile of 8192 slices costs one round of block barriers.
+constexpr int kScanItems = 8;
 __global__ void __launch_bounds__(1024) ewah_offsets_kernel(const u64* __restrict__ sizes, int64_t S,
                                                             u64* __restrict__ off,
                                                             u64* __restrict__ total) {
     __shared__ u64 warp_tot[32];
-    __shared__ u64 carry;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
-    for (int64_t tile = 0; tile < S; tile += 1024) {
-        const int64_t i = tile + threadIdx.x;
-        const u64 v = i < S ? sizes[i] : 0ull;
-        u64 incl = v;
+    constexpr int64_t kTile = 1024 * kScanItems;
+    u64 carry = 0;   // sum of all earlier tiles, kept by every thread
+    u64 v[kScanItems], nxt[kScanItems];
+    auto load = [&](int64_t tile, u64 (&dst)[kScanItems]) {
+        const int64_t base = tile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) dst[k] = (base + k < S) ? sizes[base + k] : 0ull;
+    };
+    load(0, v);
+    for (int64_t tile = 0; tile < S; tile += kTile) {
+        if (tile + kTile < S) load(tile + kTile, nxt);
+        u64 local = 0;
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) local += v[k];
+        u64 incl = local;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
             const u64 t = __shfl_up_sync(0xffffffffu, incl, d);
@@ -207,11 +218,17 @@ __global__ void __launch_bounds__(1024) ewah_offsets_kernel(const u64* __restric
             warp_tot[lane] = t;
         }
         __syncthreads();
-        const u64 before = carry + (warp ? warp_tot[warp - 1] : 0ull) + (incl - v);
-        if (i < S) off[i] = before;
-        __syncthreads();
-        if (threadIdx.x == 1023) carry = before + v;
-        __syncthreads();
+        u64 run = carry + (warp ? warp_tot[warp - 1] : 0ull) + (incl - local);
+        const int64_t base = tile + static_cast<int64_t>(threadIdx.x) * kScanItems;
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) {
+            if (base + k < S) off[base + k] = run;
+            run += v[k];
+        }
+        carry += warp_tot[31];
+        __syncthreads();   // warp_tot is rewritten by the next tile
+#pragma unroll
+        for (int k = 0; k < kScanItems; ++k) v[k] = nxt[k];
     }
     if (threadIdx.x == 0 && total != nullptr) *total = carry;
 }

@@ -450,7 +450,7 @@ __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_chunk_
 
 // Destinations of the multi-destination pack: the same int8 image / chunk scales go to each of them.
 struct MultiDst {
-    int n;
+    int n_q8, n_scales;
     int8_t* q8[BSI_B200_MAX_PEERS];
     float* scales[BSI_B200_MAX_PEERS];
 };
@@ -522,10 +522,8 @@ __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_multi_
         const float scale = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);   // 2^shift, shift <= 62
 #pragma unroll
         for (int i = 0; i < BSI_B200_MAX_PEERS; ++i) {
-            if (i < dst.n) {
-                *reinterpret_cast<u64*>(dst.q8[i] + q8_off) = packed;
-                if (lane == 0) dst.scales[i][sc_off] = scale;
-            }
+            if (i < dst.n_q8) *reinterpret_cast<u64*>(dst.q8[i] + q8_off) = packed;
+            if (i < dst.n_scales && lane == 0) dst.scales[i][sc_off] = scale;
         }
     };
 
@@ -699,6 +697,7 @@ int launch_chunk_fast(const T* x, const ChunkArgs& a) {
     if (resident <= 0) return BSI_ERR_CUDA;
     int64_t blocks = (a.rows * a.chunks + 7) / 8;
     blocks = blocks < resident ? blocks : resident;
+    if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();
     FastGeom g;
     g.total = static_cast<uint32_t>(a.rows * a.chunks);
     g.chunks = static_cast<uint32_t>(a.chunks);
@@ -796,8 +795,8 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
 }
 
 extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
-                                            int decimal_places, int bits, int n_dst, int8_t* const* q8_dst,
-                                            int64_t ld8, float* const* scale_dst, int64_t scale_ld,
+                                            int decimal_places, int bits, int n_q8_dst, int8_t* const* q8_dst,
+                                            int64_t ld8, int n_scale_dst, float* const* scale_dst, int64_t scale_ld,
                                             bsi_stream_t stream_) {
     using namespace bsi;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -805,7 +804,8 @@ extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t ro
     if (bits < 2 || bits > 8) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack_multi: bits must be in [2, 8]");
     if (dtype != BSI_DTYPE_F32 && dtype != BSI_DTYPE_F16 && dtype != BSI_DTYPE_BF16)
         return fail(BSI_ERR_INVALID, "quantize_pack_multi: unknown dtype");
-    if (n_dst < 1 || n_dst > BSI_B200_MAX_PEERS || q8_dst == nullptr || scale_dst == nullptr)
+    if (n_q8_dst < 1 || n_q8_dst > BSI_B200_MAX_PEERS || n_scale_dst < 1 || n_scale_dst > BSI_B200_MAX_PEERS ||
+        q8_dst == nullptr || scale_dst == nullptr)
         return fail(BSI_ERR_INVALID, "quantize_pack_multi: bad destinations");
     if (rows == 0 || D == 0) return BSI_OK;
     if (x == nullptr) return fail(BSI_ERR_INVALID, "quantize_pack_multi: x is null");
@@ -819,11 +819,15 @@ extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t ro
     int64_t widest = ldx > ld8 ? ldx : ld8;
     if (rows * widest >= (1ll << 31)) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack_multi: matrix too large for one launch");
     MultiDst dst = {};
-    dst.n = n_dst;
-    for (int i = 0; i < n_dst; ++i) {
-        if (q8_dst[i] == nullptr || scale_dst[i] == nullptr || (reinterpret_cast<uintptr_t>(q8_dst[i]) & 7) != 0)
-            return fail(BSI_ERR_INVALID, "quantize_pack_multi: destinations must be non-null, q8 8-byte aligned");
+    dst.n_q8 = n_q8_dst;
+    dst.n_scales = n_scale_dst;
+    for (int i = 0; i < n_q8_dst; ++i) {
+        if (q8_dst[i] == nullptr || (reinterpret_cast<uintptr_t>(q8_dst[i]) & 7) != 0)
+            return fail(BSI_ERR_INVALID, "quantize_pack_multi: q8 destinations must be non-null and 8-byte aligned");
         dst.q8[i] = q8_dst[i];
+    }
+    for (int i = 0; i < n_scale_dst; ++i) {
+        if (scale_dst[i] == nullptr) return fail(BSI_ERR_INVALID, "quantize_pack_multi: null scale destination");
         dst.scales[i] = scale_dst[i];
     }
     if (int rc = require_sm100()) return rc;
@@ -839,6 +843,7 @@ extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t ro
         if (resident <= 0) return BSI_ERR_CUDA;                                                             \
         int64_t blocks = (rows * chunks + 7) / 8;                                                           \
         blocks = blocks < resident ? blocks : resident;                                                     \
+        if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();                   \
         quantize_pack_multi_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                   \
             static_cast<const T*>(x), static_cast<uint32_t>(rows * chunks), static_cast<uint32_t>(chunks),  \
             static_cast<uint32_t>(ldx), static_cast<uint32_t>(ld8), static_cast<uint32_t>(scale_ld), dec_scale, \

@@ -77,8 +77,10 @@ class PeerExchange:
     A region is rewritten only after at least one barrier that follows its last reader on every rank,
     so one copy of each is enough."""
 
-    def __init__(self, m, rank, world, group, Q, H, Fd, dtype, device, timeout_ms=30000):
+    def __init__(self, m, rank, world, group, Q, H, Fd, dtype, device, timeout_ms=30000, push="store"):
         self.m, self.rank, self.world, self.timeout_ms = m, rank, world, int(timeout_ms)
+        self.rotate = True
+        self.push = push      # "copy": copy engines move the int8 blocks; "store": the pack kernel stores to every rank
         self.Q, self.H, self.F, self.Qn = Q, H, Fd, Q // world
         esz = torch.empty(0, dtype=dtype).element_size()
         self.esz = esz
@@ -110,6 +112,26 @@ class PeerExchange:
     def ptrs(self, name, byte_offset=0):
         """Address of region `name` (+ byte_offset) in every rank's buffer, as seen from this process."""
         return [b + self.off[name] + byte_offset for b in self.base]
+
+    def pack_to_all(self, x, dp, q8_name, sc_name, q8_off, sc_off, ld8, scale_ld, height):
+        """Packs x and leaves its int8 image at byte offset q8_off of region q8_name (row pitch ld8) and its
+        chunk scales at byte offset sc_off of sc_name (scale_ld floats per row) on every rank, then passes
+        the barrier. The scales always leave from the pack kernel; the int8 block either too ("store") or
+        lands in the own buffer and is pushed to each peer by a copy engine ("copy")."""
+        q8_ptrs, sc_ptrs = self.ptrs(q8_name, q8_off), self.ptrs(sc_name, sc_off)
+        g, G = self.rank, self.world
+        if self.push == "store":
+            # the kernel walks its destinations in list order: start each rank at its successor, so that at any
+            # moment the ranks write to different peers instead of all converging on the same one
+            order = [(g + 1 + k) % G for k in range(G)] if self.rotate else list(range(G))
+            self.m.pack_queries_multi(x, [q8_ptrs[r] for r in order], ld8, [sc_ptrs[r] for r in order], scale_ld, dp)
+        else:
+            self.m.pack_queries_multi(x, [q8_ptrs[g]], ld8, sc_ptrs, scale_ld, dp)
+            width = x.shape[1]
+            for k in range(1, G):                      # start with the next rank: the pushes fan out evenly
+                r = (g + k) % G
+                self.m.peer_copy_2d(q8_ptrs[r], ld8, q8_ptrs[g], ld8, width, height)
+        self.barrier()
 
     def barrier(self):
         self.m.peer_barrier(self.ptrs("flags"), self.rank, self.timeout_ms)
@@ -223,8 +245,7 @@ class TPDecoderLayer(nn.Module):
         hc, fc = H // 256, Fd // 256
 
         def rows_to_all(h):      # own tokens -> rows [g*Qn, (g+1)*Qn) of R on every rank
-            m.pack_queries_multi(h, px.ptrs("R_q8", g * Qn * H), H, px.ptrs("R_sc", g * Qn * hc * 4), hc, ops.dp)
-            px.barrier()
+            px.pack_to_all(h, ops.dp, "R_q8", "R_sc", g * Qn * H, g * Qn * hc * 4, H, hc, Qn)
 
         def to_owner(q8, sc, keys, bias):   # [Q, H/G] output block -> column block g of T on each token's owner
             m.linear_from_packed_scatter(q8, sc, keys, bias, ops.dp, dt, False, px.ptrs("T", g * Hl * px.esz), Qn, H)
@@ -233,14 +254,12 @@ class TPDecoderLayer(nn.Module):
         rows_to_all(self.self_attn_layer_norm(x_loc))
         qkv = ops.linear(px.R_q8, px.R_sc, self.keys_qkv, self.bias_qkv, dt)          # [Q, 3 * H/G]
         attn = self._attention(qkv, B, T)
-        m.pack_queries_multi(attn, px.ptrs("C1_q8", g * Hl), H, px.ptrs("C1_sc", g * (Hl // 256) * 4), hc, ops.dp)
-        px.barrier()
+        px.pack_to_all(attn, ops.dp, "C1_q8", "C1_sc", g * Hl, g * (Hl // 256) * 4, H, hc, px.Q)
         to_owner(px.C1_q8, px.C1_sc, self.keys_out, self.bias_out)
         x_loc = x_loc + px.T
         rows_to_all(self.final_layer_norm(x_loc))
         f = ops.linear(px.R_q8, px.R_sc, self.keys_fc1, self.bias_fc1, dt, relu=True)  # [Q, F/G]
-        m.pack_queries_multi(f, px.ptrs("C2_q8", g * Fl), Fd, px.ptrs("C2_sc", g * (Fl // 256) * 4), fc, ops.dp)
-        px.barrier()
+        px.pack_to_all(f, ops.dp, "C2_q8", "C2_sc", g * Fl, g * (Fl // 256) * 4, Fd, fc, px.Q)
         to_owner(px.C2_q8, px.C2_sc, self.keys_fc2, self.bias_fc2)
         return x_loc + px.T
 
@@ -268,15 +287,17 @@ class TPOPTForCausalLM(nn.Module):
     """OPT with tensor-parallel BSI decoder layers; embeddings, final LayerNorm and lm_head are replicated."""
 
     def __init__(self, cfg: OPTConfig, rank=0, world=1, group=None, ops=None, dtype=torch.float16, device="cuda",
-                 exchange="auto"):
+                 exchange="auto", push="store", microbatches=2):
         super().__init__()
         self.config, self.rank, self.world, self.group, self.dtype = cfg, rank, world, group, dtype
+        self.push, self.microbatches = push, int(microbatches)
         self.ops = ops if ops is not None else BsiDeviceOps()
         if exchange not in ("auto", "peer", "collective"):
             raise ValueError("exchange must be auto, peer or collective")
         # peer stores need the CUDA extension; stand-in ops (CPU tests) always use the collectives
         self.exchange = ("peer" if isinstance(self.ops, BsiDeviceOps) else "collective") if exchange == "auto" else exchange
-        self._px = None
+        self._px = {}
+        self._streams = None
         H = cfg.hidden_size
         self.embed_tokens = nn.Embedding(cfg.vocab_size, H, padding_idx=1, device=device, dtype=dtype)
         self.embed_positions = nn.Embedding(cfg.max_position_embeddings + 2, H, device=device, dtype=dtype)
@@ -284,21 +305,70 @@ class TPOPTForCausalLM(nn.Module):
         self.layers = nn.ModuleList(
             [TPDecoderLayer(cfg, rank, world, group, self.ops, dtype, device) for _ in range(cfg.num_hidden_layers)])
 
-    @torch.no_grad()
-    def _local_hidden(self, input_ids):
-        """Final-LayerNorm hidden states of the rank's own tokens, [Q/G, H]."""
-        B, T = input_ids.shape
-        Q, G = B * T, self.world
-        if Q % G != 0:
-            raise ValueError("batch x seq must divide evenly over the ranks")
+    def _stack(self, input_ids, px):
+        """Embeddings, decoder layers and final LayerNorm for the rank's own tokens of `input_ids` [b, T]."""
+        b, T = input_ids.shape
+        Q, G = b * T, self.world
         Qn = Q // G
         ids = input_ids.reshape(Q)[self.rank * Qn:(self.rank + 1) * Qn]
         pos = torch.arange(self.rank * Qn, (self.rank + 1) * Qn, device=input_ids.device) % T + 2   # OPT's offset
         x = self.embed_tokens(ids) + self.embed_positions(pos)
-        px = self._peer_exchange(Q, x.device) if (G > 1 and self.exchange == "peer") else None
         for layer in self.layers:
-            x = layer(x, B, T, px)
+            x = layer(x, b, T, px)
         return self.final_layer_norm(x)
+
+    def _micro(self, B, T):
+        """Number of micro-batches for a [B, T] input: with peer exchange the batch is split into groups of
+        sequences that run on streams of their own, so that one group's copy-engine pushes and barriers
+        overlap the other's kernels."""
+        M = self.microbatches if (self.world > 1 and self.exchange == "peer") else 1
+        while M > 1 and (B % M != 0 or ((B // M) * T // self.world) % 32 != 0):
+            M -= 1
+        return max(M, 1)
+
+    @torch.no_grad()
+    def _local_hidden(self, input_ids):
+        """Final-LayerNorm hidden states of the rank's own tokens: a list with one [Q_m/G, H] tensor per
+        micro-batch (micro-batch m holds sequences [m*B/M, (m+1)*B/M))."""
+        B, T = input_ids.shape
+        G = self.world
+        if (B * T) % G != 0:
+            raise ValueError("batch x seq must divide evenly over the ranks")
+        if not (G > 1 and self.exchange == "peer"):
+            return [self._stack(input_ids, None)]
+        M = self._micro(B, T)
+        b = B // M
+        dev = input_ids.device
+        pxs = [self._peer_exchange(m, b * T, dev) for m in range(M)]
+        if M == 1:
+            return [self._stack(input_ids, pxs[0])]
+        if self._streams is None or len(self._streams) < M:
+            self._streams = [torch.cuda.Stream(dev) for _ in range(M)]
+        cur = torch.cuda.current_stream(dev)
+        outs = []
+        for m in range(M):
+            self._streams[m].wait_stream(cur)
+        # layer by layer, alternating between the micro-batches, so that the host enqueues them interleaved
+        xs = []
+        for m in range(M):
+            with torch.cuda.stream(self._streams[m]):
+                ids_m = input_ids[m * b:(m + 1) * b]
+                Qn = b * T // G
+                ids = ids_m.reshape(b * T)[self.rank * Qn:(self.rank + 1) * Qn]
+                pos = torch.arange(self.rank * Qn, (self.rank + 1) * Qn, device=dev) % T + 2
+                xs.append(self.embed_tokens(ids) + self.embed_positions(pos))
+        for layer in self.layers:
+            for m in range(M):
+                with torch.cuda.stream(self._streams[m]):
+                    xs[m] = layer(xs[m], b, T, pxs[m])
+        for m in range(M):
+            with torch.cuda.stream(self._streams[m]):
+                out = self.final_layer_norm(xs[m])
+                out.record_stream(cur)
+                outs.append(out)
+        for m in range(M):
+            cur.wait_stream(self._streams[m])
+        return outs
 
     @torch.no_grad()
     def capture(self, B, T):
@@ -321,7 +391,7 @@ class TPOPTForCausalLM(nn.Module):
             dist.barrier(group=self.group)
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            self._g_out = self._local_hidden(self._g_ids)
+            self._g_out = self._local_hidden(self._g_ids)     # list, one tensor per micro-batch
         self._graph, self._graph_shape = graph, (B, T)
         return self
 
@@ -333,28 +403,36 @@ class TPOPTForCausalLM(nn.Module):
         if getattr(self, "_graph", None) is not None and self._graph_shape == (B, T):
             self._g_ids.copy_(input_ids, non_blocking=True)
             self._graph.replay()
-            x = self._g_out
+            parts = self._g_out
         else:
-            x = self._local_hidden(input_ids)
+            parts = self._local_hidden(input_ids)
         if G > 1:
-            full = torch.empty(Q, x.shape[1], dtype=x.dtype, device=x.device)
-            dist.all_gather_into_tensor(full, x.contiguous(), group=self.group)
-            x = full
+            fulls = []
+            for x in parts:      # token shards of one micro-batch -> all of its tokens, in sequence order
+                full = torch.empty(x.shape[0] * G, x.shape[1], dtype=x.dtype, device=x.device)
+                dist.all_gather_into_tensor(full, x.contiguous(), group=self.group)
+                fulls.append(full)
+            x = fulls[0] if len(fulls) == 1 else torch.cat(fulls, dim=0)
+        else:
+            x = parts[0]
         return x.view(B, T, -1)
 
-    def _peer_exchange(self, Q, device):
-        """The peer buffers for Q tokens (built on first use; every rank must get here with the same Q)."""
-        if self._px is not None and self._px.Q != Q:
+    def _peer_exchange(self, slot, Q, device):
+        """The peer buffers of micro-batch `slot` for Q tokens (built on first use; every rank must get here
+        with the same Q)."""
+        px = self._px.get(slot)
+        if px is not None and px.Q != Q:
             torch.cuda.synchronize(device)
             dist.barrier(group=self.group)     # nobody still writes into the buffers about to be unmapped
-            self._px.close()
-            self._px = None
-        if self._px is None:
+            px.close()
+            px = None
+        if px is None:
             if (Q // self.world) % 32 != 0:
                 raise ValueError("peer exchange needs a multiple of 32 tokens per rank")
-            self._px = PeerExchange(self.ops.m, self.rank, self.world, self.group, Q, self.config.hidden_size,
-                                    self.config.ffn_dim, self.dtype, device)
-        return self._px
+            px = PeerExchange(self.ops.m, self.rank, self.world, self.group, Q, self.config.hidden_size,
+                              self.config.ffn_dim, self.dtype, device, push=self.push)
+            self._px[slot] = px
+        return px
 
     @torch.no_grad()
     def forward(self, input_ids):
@@ -368,14 +446,15 @@ class TPOPTForCausalLM(nn.Module):
 
 @torch.no_grad()
 def build_opt_tp(name="opt-6.7b", dtype=torch.float16, device="cuda", seed=0, decimal_places=2,
-                 compress_threshold=0.5, rank=0, world=1, group=None, ops=None, exchange="auto"):
+                 compress_threshold=0.5, rank=0, world=1, group=None, ops=None, exchange="auto",
+                 push="store", microbatches=2):
     """Random-init tensor-parallel OPT. Draws every parameter from the generator `build_opt_bsi` uses for
     it (seeded by the parameter's position in the sorted HF names), so the two models hold the same
     weights, and builds the keys layer by layer so that the dense weights never sit in memory at once."""
     cfg = CONFIGS[name] if isinstance(name, str) else name
     if ops is None:
         ops = BsiDeviceOps(decimal_places, compress_threshold)
-    model = TPOPTForCausalLM(cfg, rank, world, group, ops, dtype, device, exchange)
+    model = TPOPTForCausalLM(cfg, rank, world, group, ops, dtype, device, exchange, push, microbatches)
     H, Fd, L = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers
     shapes = {"model.decoder.embed_tokens.weight": (cfg.vocab_size, H),
               "model.decoder.embed_positions.weight": (cfg.max_position_embeddings + 2, H),

@@ -71,8 +71,21 @@ def test_ewah_structured_words(W):
 
 
 def test_ewah_many_slices_offsets_scan():
-    # more slices than one scan tile (1024) so that the carry across tiles is exercised
+    # more slices than one scan tile (8192) so that the carry across tiles is exercised
     _compare(_structured(3000, 8, 7), 0.5)
+    _compare(_structured(20011, 4, 5), 0.5)
+
+
+def test_ewah_offsets_is_an_exclusive_prefix_sum():
+    import ctypes as C
+    from bsipytorch_b200 import capi
+    for S in (1, 5, 1024, 8191, 8192, 8193, 70001):
+        sizes = torch.randint(0, 300, (S,), generator=torch.Generator().manual_seed(S), dtype=torch.int64).to(DEV)
+        off = torch.full((S,), -1, dtype=torch.int64, device=DEV)
+        total = torch.full((1,), -1, dtype=torch.int64, device=DEV)
+        capi.check(capi.lib().bsi_b200_ewah_offsets(capi.ptr(sizes), S, capi.ptr(off), capi.ptr(total), capi.stream_ptr()))
+        want = torch.cumsum(sizes, 0) - sizes
+        assert torch.equal(off, want) and int(total.item()) == int(sizes.sum().item())
 
 
 def test_ewah_on_packed_activations():
