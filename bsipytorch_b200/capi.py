@@ -31,6 +31,8 @@ SIGNATURES = {
     "bsi_b200_linear_i8_act": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _i32, _i32, _vp]),
     "bsi_b200_linear_i8_scatter": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _vp, _i64, _i64, _i32, _i32, _vp]),
     "bsi_b200_quantize_pack_multi": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _i64, _i32, _vp, _i64, _vp]),
+    "bsi_b200_linear_i8_requant": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
+                                          _i32, _vp, _i64, _vp, _i64, _vp]),
     "bsi_b200_set_grid_caps": (_i32, [_i32, _i32]),
     "bsi_b200_peer_copy_2d": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "bsi_b200_peer_alloc": (_i32, [_i64, _vp, _vp]),

@@ -690,6 +690,46 @@ void linear_from_packed_scatter(torch::Tensor q8, torch::Tensor scales, py::caps
                  "bsi_b200_linear_i8_scatter");
 }
 
+// linear_from_packed whose finished output (cast + bias, optional ReLU, in `layer_dtype`) is re-quantised
+// inside the epilogue for the next linear: the int8 image goes to q8_ptrs[i] + q * ld8 + r, the chunk scales
+// to scale_ptrs[i] + 4 * (q * scale_ld + r / 256). Nothing is returned.
+void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::capsule keyset_cuda_cap,
+                                c10::optional<torch::Tensor> bias, int decimalPlaces, py::object layer_dtype, bool relu,
+                                std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
+                                int64_t scale_ld) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
+    TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
+    TORCH_CHECK(q8_ptrs.size() == scale_ptrs.size() && !q8_ptrs.empty(), "destination lists must match");
+    const int64_t Q = q8.size(0), R = keys->num_keys, chunks = keys->b.chunks;
+    TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
+    TORCH_CHECK(q8.size(1) == chunks * 256, "Word count mismatch between query batch and keys");
+    TORCH_CHECK(scales.numel() == Q * chunks, "scales shape mismatch");
+    TORCH_CHECK(decimalPlaces == keys->b.decimals, "Decimal mismatch between queries and keys");
+    const int total_decimals = decimalPlaces + keys->b.decimals;
+    const double scale_inv = total_decimals > 0 ? 1.0 / std::pow(10.0, total_decimals) : 1.0;
+    const at::ScalarType yt = torch::python::detail::py_object_to_dtype(layer_dtype);
+    TORCH_CHECK(yt == at::kHalf || yt == at::kBFloat16, "layer_dtype must be float16 or bfloat16");
+    const float* bptr = nullptr;
+    at::Tensor b32;
+    if (bias.has_value() && bias->defined()) {
+        b32 = bias->to(q8.device(), at::kFloat).contiguous();
+        TORCH_CHECK(b32.numel() == R, "bias length mismatch");
+        bptr = b32.data_ptr<float>();
+    }
+    std::vector<int8_t*> qd;
+    std::vector<float*> sd;
+    for (int64_t p : q8_ptrs) qd.push_back(reinterpret_cast<int8_t*>(static_cast<intptr_t>(p)));
+    for (int64_t p : scale_ptrs) sd.push_back(reinterpret_cast<float*>(static_cast<intptr_t>(p)));
+    check_status(bsi_b200_linear_i8_requant(q8.data_ptr<int8_t>(), q8.stride(0), scales.data_ptr<float>(), chunks,
+                                            keys->b.q8.data_ptr<int8_t>(), keys->b.q8.size(1),
+                                            keys->b.scales.data_ptr<float>(), bptr, Q, R, chunks,
+                                            static_cast<float>(scale_inv), yt == at::kHalf ? BSI_DTYPE_F16 : BSI_DTYPE_BF16,
+                                            relu ? BSI_ACT_RELU : BSI_ACT_NONE, decimalPlaces, bits_queries(),
+                                            static_cast<int>(qd.size()), qd.data(), ld8, sd.data(), scale_ld, current_stream()),
+                 "bsi_b200_linear_i8_requant");
+}
+
 py::dict debug_batch(const PackedBatch& b) {
     py::dict d;
     d["words"] = b.words;
@@ -793,6 +833,9 @@ PYBIND11_MODULE(bsi_ops, m) {
           "Bounded flag barrier over the ranks, enqueued on the current stream");
     m.def("set_grid_caps", [](int dot_sms, int pack_blocks) { check_status(bsi_b200_set_grid_caps(dot_sms, pack_blocks), "bsi_b200_set_grid_caps"); },
           py::arg("dot_sms"), py::arg("pack_blocks"), "Cap the SMs of the dot kernels / blocks of the pack kernels (0 = no cap)");
+    m.def("linear_from_packed_requant", &linear_from_packed_requant, py::arg("q8"), py::arg("scales"),
+          py::arg("keyset_cuda_cap"), py::arg("bias"), py::arg("decimal_places"), py::arg("layer_dtype"), py::arg("relu"),
+          py::arg("q8_ptrs"), py::arg("ld8"), py::arg("scale_ptrs"), py::arg("scale_ld"));
     m.def("peer_copy_2d", &peer_copy_2d, py::arg("dst"), py::arg("dst_pitch"), py::arg("src"), py::arg("src_pitch"),
           py::arg("width_bytes"), py::arg("height"));
     m.def("pack_queries_multi", &pack_queries_multi, py::arg("x2d"), py::arg("q8_ptrs"), py::arg("ld8"),

@@ -53,6 +53,18 @@ struct ScatterDst {
     void* y[BSI_B200_MAX_PEERS];      // row q -> y[q / rows_per_dst], local row q % rows_per_dst
 };
 
+// Destinations of a linear that re-quantises its finished output (n = 0: off). The output row block of a
+// tile is one 256-column chunk per row, so its chunk scale is known inside the tile.
+struct RequantDst {
+    int n;                 // destinations (own buffer and peer mappings alike)
+    int bits;              // 7 for activations
+    float mult;            // 10^decimal_places, at most 1000
+    int64_t ld8;           // row pitch of the int8 matrices (bytes)
+    int64_t scale_ld;      // floats per row of the scale matrices
+    int8_t* q8[BSI_B200_MAX_PEERS];      // already offset to this linear's first output column
+    float* scales[BSI_B200_MAX_PEERS];   // already offset to this linear's first output chunk
+};
+
 // Reads and clears the status word of the peer barrier kernels (0 = clean, 64 + p = gave up waiting for rank p).
 int take_peer_status(int* v);
 

@@ -15,7 +15,7 @@ int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_st
 int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride, const int8_t* k8, int64_t ldk,
                 const float* bw0, const float* bias, int64_t Q, int64_t R, int64_t chunks, float scale_inv,
                 void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, int relu,
-                const ScatterDst* scatter, cudaStream_t stream);
+                const ScatterDst* scatter, const RequantDst* requant, cudaStream_t stream);
 
 int dot_words_bmma(const uint64_t* A, const float* qs, int64_t qs_stride, int Sa, int64_t W,
                    const uint64_t* B, const float* Bw, int Sb, int64_t R, int64_t Q, float scale_inv,
@@ -166,7 +166,7 @@ extern "C" int bsi_b200_linear_i8_act(const int8_t* a8, int64_t lda, const float
         return fail(BSI_ERR_INVALID, "linear_i8: unknown y_dtype");
     if (int rc = require_sm100()) return rc;
     return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, bias, Q, R, chunks, scale_inv, y, ldy, y_dtype,
-                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, nullptr, static_cast<cudaStream_t>(stream_));
+                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, nullptr, nullptr, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int bsi_b200_linear_i8_scatter(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
@@ -204,7 +204,51 @@ extern "C" int bsi_b200_linear_i8_scatter(const int8_t* a8, int64_t lda, const f
     }
     if (int rc = require_sm100()) return rc;
     return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, bias, Q, R, chunks, scale_inv, nullptr, ldy, y_dtype,
-                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, &sc, static_cast<cudaStream_t>(stream_));
+                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, &sc, nullptr, static_cast<cudaStream_t>(stream_));
+}
+
+extern "C" int bsi_b200_linear_i8_requant(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                                          const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                                          int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                                          int layer_dtype, int activation, int decimal_places, int bits,
+                                          int n_dst, int8_t* const* q8_dst, int64_t ld8,
+                                          float* const* scale_dst, int64_t scale_ld, bsi_stream_t stream_) {
+    using namespace bsi;
+    if (Q < 0 || R < 0 || chunks < 0) return fail(BSI_ERR_INVALID, "linear_i8_requant: negative size");
+    if (Q == 0 || R == 0) return BSI_OK;
+    if (a8 == nullptr || k8 == nullptr || qs == nullptr || bw0 == nullptr || q8_dst == nullptr || scale_dst == nullptr)
+        return fail(BSI_ERR_INVALID, "linear_i8_requant: null pointer");
+    if (chunks == 0) return fail(BSI_ERR_INVALID, "linear_i8_requant: chunks must be positive");
+    if (lda < chunks * 256 || ldk < chunks * 256 || (lda & 15) || (ldk & 15) ||
+        (reinterpret_cast<uintptr_t>(a8) & 15) || (reinterpret_cast<uintptr_t>(k8) & 15))
+        return fail(BSI_ERR_INVALID, "linear_i8_requant: a8/k8 need 16-byte aligned rows of at least 256*chunks bytes");
+    if (qs_stride != 0 && qs_stride < chunks) return fail(BSI_ERR_INVALID, "linear_i8_requant: qs_stride < chunks");
+    if (activation != BSI_ACT_NONE && activation != BSI_ACT_RELU)
+        return fail(BSI_ERR_INVALID, "linear_i8_requant: unknown activation");
+    if (layer_dtype != BSI_DTYPE_F16 && layer_dtype != BSI_DTYPE_BF16)
+        return fail(BSI_ERR_UNSUPPORTED, "linear_i8_requant: the layer type must be float16 or bfloat16");
+    if ((R & 255) != 0) return fail(BSI_ERR_UNSUPPORTED, "linear_i8_requant: R must be a multiple of 256");
+    if (bits < 2 || bits > 8) return fail(BSI_ERR_UNSUPPORTED, "linear_i8_requant: bits must be in [2, 8]");
+    if (decimal_places < 0 || decimal_places > 3)
+        return fail(BSI_ERR_UNSUPPORTED, "linear_i8_requant: decimal_places must be in [0, 3]");
+    if (n_dst < 1 || n_dst > BSI_B200_MAX_PEERS || ld8 < R || (ld8 & 15) != 0 || scale_ld < R / 256)
+        return fail(BSI_ERR_INVALID, "linear_i8_requant: bad destinations (ld8 >= R, ld8 % 16 == 0, scale_ld >= R/256)");
+    RequantDst rq = {};
+    rq.n = n_dst;
+    rq.bits = bits;
+    rq.mult = 1.0f;
+    for (int i = 0; i < decimal_places; ++i) rq.mult *= 10.0f;
+    rq.ld8 = ld8;
+    rq.scale_ld = scale_ld;
+    for (int i = 0; i < n_dst; ++i) {
+        if (q8_dst[i] == nullptr || scale_dst[i] == nullptr || (reinterpret_cast<uintptr_t>(q8_dst[i]) & 15) != 0)
+            return fail(BSI_ERR_INVALID, "linear_i8_requant: destinations must be non-null, q8 16-byte aligned");
+        rq.q8[i] = q8_dst[i];
+        rq.scales[i] = scale_dst[i];
+    }
+    if (int rc = require_sm100()) return rc;
+    return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, bias, Q, R, chunks, scale_inv, q8_dst[0], R, layer_dtype,
+                       nullptr, 0, activation == BSI_ACT_RELU ? 1 : 0, nullptr, &rq, static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int bsi_b200_linear_i8(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,

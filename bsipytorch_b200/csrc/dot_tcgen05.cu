@@ -28,6 +28,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "quant_bytes.cuh"
 
 namespace bsi {
 
@@ -428,12 +429,13 @@ int launch_tile(const CUtensorMap& ma, const CUtensorMap& mb, const float* qs, i
     return check_launch("dot_i8 tcgen05 launch");
 }
 
-template <int BN, bool DBG, typename OutT>
+template <int BN, bool DBG, typename OutT, bool REQ = false>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
                 const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
-                float scale_inv, void* out, int64_t ldo, int32_t* dbg, const ScatterDst& scatter, cudaStream_t stream) {
+                float scale_inv, void* out, int64_t ldo, int32_t* dbg, const ScatterDst& scatter,
+                const RequantDst& requant, cudaStream_t stream) {
     using C = pair::Cfg<BN>;
-    static int max_clusters[64] = {0};
+    static int max_clusters[64] = {0};   // per instantiation
     int dev = 0;
     BSI_CUDA_TRY(cudaGetDevice(&dev));
     const int tiles_m = (Q + 255) / 256;
@@ -453,18 +455,18 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     int resident = 0;
     if (dev >= 0 && dev < 64) resident = max_clusters[dev];
     if (resident == 0) {
-        BSI_CUDA_TRY(cudaFuncSetAttribute(pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>,
+        BSI_CUDA_TRY(cudaFuncSetAttribute(pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT, REQ>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
         cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
-        BSI_CUDA_TRY(cudaOccupancyMaxActiveClusters(&resident, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>, &cfg));
+        BSI_CUDA_TRY(cudaOccupancyMaxActiveClusters(&resident, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT, REQ>, &cfg));
         if (resident <= 0) return fail(BSI_ERR_CUDA, "dot_i8: no cluster of 2 CTAs fits on this device");
         if (dev >= 0 && dev < 64) max_clusters[dev] = resident;
     }
     int pairs = tiles_total < resident ? tiles_total : resident;
     if (dot_sm_cap() > 1 && pairs > dot_sm_cap() / 2) pairs = dot_sm_cap() / 2;   // leave SMs to concurrent streams
     cfg.gridDim = dim3(2 * pairs, 1, 1);
-    BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT>, ma, mb, vector_store, qs,
-                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter));
+    BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT, REQ>, ma, mb, vector_store, qs,
+                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter, requant));
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
@@ -514,7 +516,15 @@ int pick_bn(int64_t Q, int64_t R) {
 int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride, const int8_t* k8, int64_t ldk,
                 const float* bw0, const float* bias, int64_t Q, int64_t R, int64_t chunks, float scale_inv,
                 void* out, int64_t ldo, int y_dtype, int32_t* dbg_iacc, int force_bn, int relu,
-                const ScatterDst* scatter_in, cudaStream_t stream) {
+                const ScatterDst* scatter_in, const RequantDst* requant_in, cudaStream_t stream) {
+    RequantDst requant = {};
+    if (requant_in != nullptr) {
+        requant = *requant_in;
+        if (requant.n < 1 || requant.n > BSI_B200_MAX_PEERS || (R & 255) != 0 ||
+            (y_dtype != BSI_DTYPE_F16 && y_dtype != BSI_DTYPE_BF16) || dbg_iacc != nullptr || scatter_in != nullptr)
+            return fail(BSI_ERR_INVALID, "dot_i8: re-quantised output needs R % 256 == 0 and a 16-bit layer type");
+        force_bn = 256;   // one tile row = one 256-column chunk
+    }
     ScatterDst scatter = {};
     if (scatter_in != nullptr) {
         scatter = *scatter_in;
@@ -542,12 +552,19 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
 #define BSI_PAIR_T(BN_, DBG_, T_)                                                                              \
     launch_pair<BN_, DBG_, T_>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv, out, ldo,  \
-                               dbg_iacc, scatter, stream)
+                               dbg_iacc, scatter, requant, stream)
 #define BSI_PAIR(BN_)                                                                   \
     (y_dtype == BSI_DTYPE_F16    ? BSI_PAIR_T(BN_, false, __half)                       \
      : y_dtype == BSI_DTYPE_BF16 ? BSI_PAIR_T(BN_, false, __nv_bfloat16)                \
      : dbg_iacc                  ? BSI_PAIR_T(BN_, true, float)                         \
                                  : BSI_PAIR_T(BN_, false, float))
+    if (requant.n > 0) {
+        if (y_dtype == BSI_DTYPE_F16)
+            return launch_pair<256, false, __half, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv,
+                                                         out, ldo, nullptr, scatter, requant, stream);
+        return launch_pair<256, false, __nv_bfloat16, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c,
+                                                            scale_inv, out, ldo, nullptr, scatter, requant, stream);
+    }
     switch (bn) {
         case 256: return BSI_PAIR(256);
         case 128: return BSI_PAIR(128);
@@ -566,7 +583,7 @@ int dot_i8_tcgen05(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_st
     const bool want_pair = force_bn ? (force_bn >= 2000) : (Q > 128);
     if (want_pair) {
         return dot_i8_pair(a8, lda, qs, qs_stride, k8, ldk, bw0, nullptr, Q, R, chunks, scale_inv, out, ldo,
-                           BSI_DTYPE_F32, dbg_iacc, force_bn ? force_bn - 2000 : 0, /*relu=*/0, nullptr, stream);
+                           BSI_DTYPE_F32, dbg_iacc, force_bn ? force_bn - 2000 : 0, /*relu=*/0, nullptr, nullptr, stream);
     }
     const int bn = force_bn ? force_bn : pick_bn(Q, R);
     CUtensorMap ma, mb;

@@ -48,7 +48,9 @@ struct Cfg {
     static constexpr int kTmemCols = 512;                 // all of TMEM: 1 CTA per SM anyway
     static constexpr int kAccBufs = 512 / BN;             // accumulator ring: 2, 4 or 8 buffers of BN columns
     static constexpr int kBarriers = 2 * kStages + 2 * kAccBufs + 1;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarriers * 8 + 16 + 1024;
+    // chunk-maximum exchange of the re-quantising epilogue: 2 parities x 8 warps x 32 lanes x 2 bytes + 8 counters
+    static constexpr int kXchgBytes = 2 * kEpiWarps * 32 * 2 + kEpiWarps * 4;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarriers * 8 + 16 + kXchgBytes + 1024;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -174,13 +176,14 @@ __device__ __forceinline__ OutT relu_if(OutT v, bool relu) {
     return (relu && static_cast<float>(v) < 0.0f) ? static_cast<OutT>(0.0f) : v;
 }
 
-template <int BN, bool DBG, typename OutT>
+template <int BN, bool DBG, typename OutT, bool REQ = false>
 __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
     int store_flags,   // bit 0: 16-byte vector stores are possible; bit 1: ReLU on the finished value
     const float* __restrict__ qs, int64_t qs_stride, const float* __restrict__ bw0,
     const float* __restrict__ bias, int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
-    void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc, const ScatterDst scatter) {
+    void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc, const ScatterDst scatter,
+    const RequantDst requant) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     constexpr int kCols = BN / 2;       // accumulator columns per epilogue warp
@@ -192,6 +195,8 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     uint64_t* bars = reinterpret_cast<uint64_t*>(store_area + C::kStoreBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kBarriers);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    uint16_t* xchg_vals = reinterpret_cast<uint16_t*>(tmem_slot + 4);                       // [2][kEpiWarps][32]
+    volatile uint32_t* xchg_count = reinterpret_cast<volatile uint32_t*>(xchg_vals + 2 * kEpiWarps * 32);   // [kEpiWarps]
 
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_base = smem_u32(bars);
@@ -230,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
         }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
+        for (int w = 0; w < kEpiWarps; ++w) xchg_count[w] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -329,6 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
         float acc[kCols];
         int cc = 0;
         bool ok = true;
+        uint32_t tiles_done = 0;   // tiles this warp has re-quantised (the chunk-maximum exchange counts them)
         for (int tile = pair_id; tile < tiles_total && ok; tile += num_pairs) {
             const int tm = tile % tiles_m;
             const int tn = tile / tiles_m;
@@ -402,6 +409,113 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
             constexpr int kChunks = kRoundCols * E / 16;                        // 8, or 4 for 64-byte rows
             constexpr int kRounds = kCols / kRoundCols;
             constexpr int kRowBytes = kChunks * 16;
+            if constexpr (REQ) {
+                static_assert(BN == 256 && !DBG && sizeof(OutT) == 2, "re-quantisation: 256-wide tiles, 16-bit layer type");
+                {
+                    // ---- fused re-quantisation: the finished value in the layer's type (cast + bias, ReLU) is
+                    // what the next linear's packer would read; with BN = 256 a tile row is exactly one chunk,
+                    // split between this warp and the warp of the other column half. Same integers as the pack
+                    // kernel's fast path (the values have 16-bit precision, so the float32 rounding is exact).
+                    uint32_t amax_bits = 0;
+#pragma unroll
+                    for (int j = 0; j < kCols; ++j) {
+                        const float w = __shfl_sync(0xffffffffu, bwreg[j & 3], j >> 2);
+                        const float bv = __shfl_sync(0xffffffffu, biasreg[j & 3], j >> 2);
+                        // cast, then add the bias rounded to the layer type (0 without bias: the sum is then the
+                        // value itself), round again: what finish<OutT> computes, without its branch on has_bias
+                        float v = static_cast<float>(static_cast<OutT>((acc[j] * w) * scale_inv));
+                        v = static_cast<float>(static_cast<OutT>(v + static_cast<float>(static_cast<OutT>(bv))));
+                        if (relu && v < 0.0f) v = 0.0f;
+                        acc[j] = v;
+                        amax_bits = max(amax_bits, __float_as_uint(v) & 0x7fffffffu);
+                        if ((j & 15) == 15) asm volatile("" ::: "memory");   // keeps the 128 steps from being interleaved
+                    }
+                    // Largest magnitude of the whole chunk: swap with the partner warp (same rows, other column
+                    // half). The value is one of the OutT values, so its 16-bit pattern carries it exactly. Each
+                    // warp publishes into its slot of parity (tiles_done & 1) and bumps its counter; a slot is
+                    // rewritten two tiles later, after the partner's next publication, which follows its read.
+                    // The wait is bounded like every other wait of the kernel.
+                    {
+                        const uint32_t par = tiles_done & 1u;
+                        const OutT amax_t = static_cast<OutT>(__uint_as_float(amax_bits));
+                        xchg_vals[(par * kEpiWarps + ew) * 32 + lane] = *reinterpret_cast<const uint16_t*>(&amax_t);
+                        __syncwarp();
+                        if (lane == 0) {
+                            __threadfence_block();
+                            xchg_count[ew] = tiles_done + 1u;
+                        }
+                        const long long t0 = clock64();
+                        while (static_cast<int32_t>(xchg_count[ew ^ 4] - (tiles_done + 1u)) < 0) {
+                            if (*actx.flag || clock64() - t0 > kWait) {
+                                *actx.flag = 1;
+                                store_flag_cluster(actx.peer_flag, 1);
+                                atomicCAS(&g_device_status, 0, 16 + 7);
+                                ok = false;
+                                break;
+                            }
+                        }
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (!ok) break;
+                        __threadfence_block();
+                        const uint16_t other = xchg_vals[(par * kEpiWarps + (ew ^ 4)) * 32 + lane];
+                        const OutT other_t = *reinterpret_cast<const OutT*>(&other);
+                        amax_bits = max(amax_bits, __float_as_uint(static_cast<float>(other_t)) & 0x7fffffffu);
+                        ++tiles_done;
+                    }
+                    float ymax = __uint_as_float(amax_bits) * requant.mult;
+                    if (!(amax_bits < 0x7f800000u && ymax < 8388608.0f)) {
+                        // NaN / inf / out of the exact range: not representable on this path; report, store zeros
+                        atomicCAS(&g_device_status, 0, 48);
+                        ymax = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < kCols; ++j) acc[j] = 0.0f;
+                    }
+                    const int shift = fast_shift(ymax, requant.bits);
+                    float inv, cst;
+                    fast_round_consts(shift, inv, cst);
+                    // stage 32 rows x 128 bytes through this warp's 4 KB (16-byte chunks XOR-swizzled by row)
+                    uint8_t* dst = my_store + lane * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        uint32_t wv[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const int j = ch * 16 + k * 4;
+                            wv[k] = sign_clamp4(fast_magnitude(acc[j], requant.mult, inv, cst),
+                                                fast_magnitude(acc[j + 1], requant.mult, inv, cst),
+                                                fast_magnitude(acc[j + 2], requant.mult, inv, cst),
+                                                fast_magnitude(acc[j + 3], requant.mult, inv, cst),
+                                                __float_as_uint(acc[j]), __float_as_uint(acc[j + 1]),
+                                                __float_as_uint(acc[j + 2]), __float_as_uint(acc[j + 3]), requant.bits);
+                        }
+                        *reinterpret_cast<uint4*>(dst + ((ch ^ (lane & 7)) << 4)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                    }
+                    __syncwarp();
+                    const int cchunk = lane & 7;
+                    const int col = n0 + col0 + cchunk * 16;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + (lane >> 3);
+                        const uint4 o = *reinterpret_cast<const uint4*>(my_store + rr * 128 + ((cchunk ^ (rr & 7)) << 4));
+                        const int grow = row_base + rr;
+                        if (grow < Q) {
+                            const int64_t off = static_cast<int64_t>(grow) * requant.ld8 + col;
+#pragma unroll
+                            for (int d = 0; d < BSI_B200_MAX_PEERS; ++d)
+                                if (d < requant.n) *reinterpret_cast<uint4*>(requant.q8[d] + off) = o;
+                        }
+                    }
+                    if (half == 0 && row_ok) {
+                        const float scale = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);   // 2^shift
+                        const int64_t off = static_cast<int64_t>(row) * requant.scale_ld + (n0 >> 8);
+#pragma unroll
+                        for (int d = 0; d < BSI_B200_MAX_PEERS; ++d)
+                            if (d < requant.n) requant.scales[d][off] = scale;
+                    }
+                    __syncwarp();
+                    continue;
+                }
+            }
             OutT* outp = static_cast<OutT*>(out);
             int row_shift = 0;   // first global row of the destination matrix this warp's 32 rows belong to
             if (scatter.n > 0) {

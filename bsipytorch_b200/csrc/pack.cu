@@ -15,6 +15,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "quant_bytes.cuh"
 
 namespace bsi {
 namespace {
@@ -170,37 +171,14 @@ __device__ __forceinline__ uint32_t decimal_round_mag32(uint32_t fbits, uint32_t
     return sh >= 32u ? 0u : ((P + (1u << (sh - 1u))) >> sh);
 }
 
-// prmt.b32 with the full 4-bit selectors (values 8..15 replicate the sign bit of the chosen byte over the
-// result byte; the __byte_perm intrinsic only honours 3 bits per selector).
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t d;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
-    return d;
-}
-
 // Byte-wise tail of the fast paths: u[e] carries the unsigned quantised magnitude of element e in its
-// low byte (0 .. 2^(bits-1)), f[e] the sign. Clamps positives to 2^(bits-1)-1, negates the negatives and
-// returns the 8 two's-complement bytes, four elements per 32-bit register operation.
+// low byte (0 .. 2^(bits-1)), f[e] the sign; returns the 8 two's-complement bytes.
 __device__ __forceinline__ u64 sign_clamp_bytes(const uint32_t (&u)[8], const float (&f)[8], int bits) {
-    const uint32_t top = 0x01010101u << (bits - 1);
-    uint32_t out[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int e = 4 * h;
-        // low bytes of u[e..e+3]
-        uint32_t w = __byte_perm(__byte_perm(u[e], u[e + 1], 0x0040), __byte_perm(u[e + 2], u[e + 3], 0x0040), 0x5410);
-        // 0xff per negative element
-        const uint32_t m = prmt(prmt(__float_as_uint(f[e]), __float_as_uint(f[e + 1]), 0x00fbu),
-                                prmt(__float_as_uint(f[e + 2]), __float_as_uint(f[e + 3]), 0x00fbu), 0x5410u);
-        // positive 2^(bits-1) -> 2^(bits-1) - 1 (the byte is exactly `top` there, so the borrow stays inside it)
-        const uint32_t over = w & ~m & top;
-        w -= over >> (bits - 1);
-        // negate the bytes under m: (~b + 1) per byte, the carry kept inside the byte by adding in 7 bits
-        const uint32_t x = w ^ m;
-        const uint32_t t = (x & 0x7f7f7f7fu) + (m & 0x01010101u);
-        out[h] = t ^ (x & 0x80808080u);
-    }
-    return static_cast<u64>(out[0]) | (static_cast<u64>(out[1]) << 32);
+    const uint32_t lo = sign_clamp4(u[0], u[1], u[2], u[3], __float_as_uint(f[0]), __float_as_uint(f[1]),
+                                    __float_as_uint(f[2]), __float_as_uint(f[3]), bits);
+    const uint32_t hi = sign_clamp4(u[4], u[5], u[6], u[7], __float_as_uint(f[4]), __float_as_uint(f[5]),
+                                    __float_as_uint(f[6]), __float_as_uint(f[7]), bits);
+    return static_cast<u64>(lo) | (static_cast<u64>(hi) << 32);
 }
 
 // One (row, chunk) unit on the generic path (any decimal_places, any magnitude, NaN/inf, any layout):
@@ -269,16 +247,11 @@ __device__ __forceinline__ bool fast_quantise(const float (&f)[8], uint32_t dec_
         const float fmult = static_cast<float>(dec_mult);
         const float ymax = __uint_as_float(amax_bits) * fmult;
         if (!(amax_bits < 0x7f800000u && ymax < 8388608.0f)) return false;
-        const uint32_t mx = __float2uint_rz(ymax + 0.5f);   // rounding is monotonic: the largest |v|
-        shift = (32 - __clz(static_cast<int>(mx))) - (bits - 1);
-        shift = shift < 0 ? 0 : shift;
-        const float inv = __uint_as_float(static_cast<uint32_t>(127 - shift) << 23);   // 2^-shift
-        const float c = (shift > 0 ? 0.5f : 0.0f) - 8388608.0f * inv;
+        shift = fast_shift(ymax, bits);   // rounding is monotonic: half_away(ymax) is the largest |v|
+        float inv, c;
+        fast_round_consts(shift, inv, c);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float r1 = __fadd_rz(fmaf(fabsf(f[e]), fmult, 0.5f), 8388608.0f);
-            u[e] = __float_as_uint(__fadd_rz(fmaf(r1, inv, c), 8388608.0f));
-        }
+        for (int e = 0; e < 8; ++e) u[e] = fast_magnitude(f[e], fmult, inv, c);
     } else {
         if (!(amax_bits < (150u << 23))) return false;
         const uint32_t mx = decimal_round_mag32(amax_bits, dec_mult);

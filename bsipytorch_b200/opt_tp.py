@@ -61,6 +61,12 @@ class BsiDeviceOps:
     def linear(self, q8, scales, keys, bias, out_dtype, relu=False):
         return self.m.linear_from_packed(q8, scales, keys, bias, self.dp, out_dtype, relu)
 
+    def linear_requant(self, q8, scales, keys, bias, layer_dtype, relu, q8_ptrs, ld8, scale_ptrs, scale_ld):
+        """Linear whose output is re-quantised for the next linear inside its epilogue and stored to the given
+        addresses (needs a 16-bit layer type and a multiple of 256 output features)."""
+        self.m.linear_from_packed_requant(q8, scales, keys, bias, self.dp, layer_dtype, relu, q8_ptrs, ld8,
+                                          scale_ptrs, scale_ld)
+
 
 def _align(n: int, a: int = 256) -> int:
     return -(-n // a) * a
@@ -163,6 +169,9 @@ class TPDecoderLayer(nn.Module):
         self.h_lo, self.h_hi = _block(H, world, rank, 256 if world > 1 else 1, "hidden_size")
         self.f_lo, self.f_hi = _block(Fd, world, rank, 256 if world > 1 else 1, "ffn_dim")
         self.local_heads = cfg.num_attention_heads // world
+        # fc1 -> ReLU -> re-quantise inside the fc1 epilogue: CUDA extension, 16-bit layer type, whole chunks per rank
+        self.fuse_requant = (isinstance(ops, BsiDeviceOps) and dtype in (torch.float16, torch.bfloat16)
+                             and (self.f_hi - self.f_lo) % 256 == 0 and ops.dp <= 3)
         self.self_attn_layer_norm = nn.LayerNorm(H, device=device, dtype=dtype)
         self.final_layer_norm = nn.LayerNorm(H, device=device, dtype=dtype)
         self.keys_qkv = self.keys_out = self.keys_fc1 = self.keys_fc2 = None
@@ -258,8 +267,16 @@ class TPDecoderLayer(nn.Module):
         to_owner(px.C1_q8, px.C1_sc, self.keys_out, self.bias_out)
         x_loc = x_loc + px.T
         rows_to_all(self.final_layer_norm(x_loc))
-        f = ops.linear(px.R_q8, px.R_sc, self.keys_fc1, self.bias_fc1, dt, relu=True)  # [Q, F/G]
-        px.pack_to_all(f, ops.dp, "C2_q8", "C2_sc", g * Fl, g * (Fl // 256) * 4, Fd, fc, px.Q)
+        if self.fuse_requant:
+            # fc1 -> ReLU -> re-quantise in the fc1 epilogue, stored into C2 of every rank while the dot runs
+            order = [(g + 1 + k) % self.world for k in range(self.world)]
+            q8p, scp = px.ptrs("C2_q8", g * Fl), px.ptrs("C2_sc", g * (Fl // 256) * 4)
+            ops.linear_requant(px.R_q8, px.R_sc, self.keys_fc1, self.bias_fc1, dt, True, [q8p[r] for r in order], Fd,
+                               [scp[r] for r in order], fc)
+            px.barrier()
+        else:
+            f = ops.linear(px.R_q8, px.R_sc, self.keys_fc1, self.bias_fc1, dt, relu=True)  # [Q, F/G]
+            px.pack_to_all(f, ops.dp, "C2_q8", "C2_sc", g * Fl, g * (Fl // 256) * 4, Fd, fc, px.Q)
         to_owner(px.C2_q8, px.C2_sc, self.keys_fc2, self.bias_fc2)
         return x_loc + px.T
 
@@ -277,8 +294,15 @@ class TPDecoderLayer(nn.Module):
         x_loc = x_loc + self._to_token_shard(o)
         h = self.final_layer_norm(x_loc)
         q8, sc = self._pack_gather_rows(h, Q)
-        f = ops.linear(q8, sc, self.keys_fc1, self.bias_fc1, dt, relu=True)           # [Q, F/G]
-        q8, sc = self._pack_gather_cols(f)
+        if self.fuse_requant and self.world == 1:
+            Fd = self.cfg.ffn_dim
+            q8f = torch.empty(Q, Fd, dtype=torch.int8, device=x_loc.device)
+            scf = torch.empty(Q, Fd // 256, dtype=torch.float32, device=x_loc.device)
+            ops.linear_requant(q8, sc, self.keys_fc1, self.bias_fc1, dt, True, [q8f.data_ptr()], Fd, [scf.data_ptr()], Fd // 256)
+            q8, sc = q8f, scf
+        else:
+            f = ops.linear(q8, sc, self.keys_fc1, self.bias_fc1, dt, relu=True)       # [Q, F/G]
+            q8, sc = self._pack_gather_cols(f)
         o = ops.linear(q8, sc, self.keys_fc2, self.bias_fc2, dt)                      # [Q, H/G]
         return x_loc + self._to_token_shard(o)
 

@@ -152,6 +152,23 @@ int bsi_b200_peer_close(void* peer_ptr);
  * 64 + the missing rank (bsi_b200_device_status), so a lost rank cannot hang the GPU. */
 int bsi_b200_peer_barrier(uint32_t* const* flags, int rank, int n, int64_t timeout_ms, bsi_stream_t stream);
 
+/* Linear whose finished output is re-quantised for the next linear inside the epilogue, so that the
+ * layer-type [Q, R] matrix is never written: y = activation(cast(out) + cast(bias)) in layer_dtype
+ * (BSI_DTYPE_F16 / BF16) is what bsi_b200_linear_i8_act would store; here every 256-column chunk of y
+ * is quantised as bsi_b200_quantize_pack (chunk mode, `bits`, decimal_places) would quantise it and the
+ * int8 image / chunk scales go to n_dst places: q8_dst[i] + q * ld8 + r and
+ * scale_dst[i] + q * scale_ld + r / 256 (pointers already offset to this linear's first output column /
+ * chunk; own memory or peer mappings). Same integers as the two-kernel sequence. R % 256 == 0,
+ * decimal_places in [0, 3]; a chunk holding NaN, inf or |y * 10^dp| >= 2^23 cannot be expressed on this
+ * path: it is stored as zeros and the device status is set to 48 (bsi_b200_device_status).
+ * OPT: fc1 -> ReLU -> fc2 (the reference runs dot, two elementwise kernels, ReLU and the fc2 packer). */
+int bsi_b200_linear_i8_requant(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_stride,
+                               const int8_t* k8, int64_t ldk, const float* bw0, const float* bias,
+                               int64_t Q, int64_t R, int64_t chunks, float scale_inv,
+                               int layer_dtype, int activation, int decimal_places, int bits,
+                               int n_dst, int8_t* const* q8_dst, int64_t ld8,
+                               float* const* scale_dst, int64_t scale_ld, bsi_stream_t stream);
+
 /* Process-wide caps on the grids of the persistent kernels, 0 = none (the default): dot_sms limits
  * the SMs the dot / linear kernels occupy (pairs of CTAs, so the even part counts), pack_blocks the
  * blocks of a pack launch. With several streams in flight (micro-batches of the tensor-parallel

@@ -196,3 +196,59 @@ def test_linear_i8_fuses_cast_and_bias(dtype, shape):
         capi.check(L.bsi_b200_cast_bias(capi.ptr(out), R, capi.ptr(b), Q, R, capi.ptr(y2), R, code, capi.stream_ptr()))
         assert torch.equal(y2, want)
     assert capi.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("Q,R,D,relu", [(300, 512, 1024, True), (64, 256, 256, False), (513, 768, 512, True)])
+def test_linear_requant_equals_linear_then_pack(dtype, Q, R, D, relu):
+    """The re-quantising epilogue stores the integers and chunk scales that the pack kernel derives from the
+    layer-type output of the plain fused linear (cast + bias, optional ReLU)."""
+    from bsipytorch_b200 import bsi_ops
+
+    g = torch.Generator().manual_seed(Q + R + D)
+    x = (torch.randn(Q, D, generator=g) * torch.where(torch.rand(Q, D, generator=g) < 0.01, 20.0, 1.0)).to(dtype).to(DEV)
+    w = (torch.randn(R, D, generator=g) * 0.05).to(DEV)
+    bias = torch.randn(R, generator=g).to(DEV)
+    cap = bsi_ops.build_bsi_keys_cuda(w, 2, 0.5)[0]
+    q8 = torch.empty(Q, D, dtype=torch.int8, device=DEV)
+    sc = torch.empty(Q, D // 256, dtype=torch.float32, device=DEV)
+    bsi_ops.pack_queries_into(x, q8, sc, 2)
+    y = bsi_ops.linear_from_packed(q8, sc, cap, bias, 2, dtype, relu)
+    want_q8 = torch.empty(Q, R, dtype=torch.int8, device=DEV)
+    want_sc = torch.empty(Q, R // 256, dtype=torch.float32, device=DEV)
+    bsi_ops.pack_queries_into(y, want_q8, want_sc, 2)
+    # two destinations at once
+    got_q8 = torch.full((2, Q, R), 99, dtype=torch.int8, device=DEV)
+    got_sc = torch.full((2, Q, R // 256), -1.0, dtype=torch.float32, device=DEV)
+    bsi_ops.linear_from_packed_requant(q8, sc, cap, bias, 2, dtype, relu, [got_q8[0].data_ptr(), got_q8[1].data_ptr()], R,
+                                       [got_sc[0].data_ptr(), got_sc[1].data_ptr()], R // 256)
+    # a column block of a wider matrix
+    wide_q8 = torch.full((Q, 2 * R), 99, dtype=torch.int8, device=DEV)
+    wide_sc = torch.full((Q, 2 * (R // 256)), -1.0, dtype=torch.float32, device=DEV)
+    bsi_ops.linear_from_packed_requant(q8, sc, cap, bias, 2, dtype, relu, [wide_q8.data_ptr() + R], 2 * R,
+                                       [wide_sc.data_ptr() + 4 * (R // 256)], 2 * (R // 256))
+    assert bsi_ops.device_status() == 0
+    for i in range(2):
+        assert torch.equal(got_sc[i], want_sc)
+        assert torch.equal(got_q8[i], want_q8)
+    assert torch.equal(wide_q8[:, R:], want_q8) and torch.equal(wide_sc[:, R // 256:], want_sc)
+    assert (wide_q8[:, :R] == 99).all() and (wide_sc[:, : R // 256] == -1.0).all()
+    assert (want_q8 != 0).any()
+
+
+def test_linear_requant_reports_values_it_cannot_express():
+    from bsipytorch_b200 import bsi_ops
+
+    x = torch.full((32, 256), 60000.0, dtype=torch.float16, device=DEV)        # the dot overflows float16: inf
+    w = torch.full((256, 256), 0.3, device=DEV)
+    cap = bsi_ops.build_bsi_keys_cuda(w, 2, 0.5)[0]
+    q8 = torch.empty(32, 256, dtype=torch.int8, device=DEV)
+    sc = torch.empty(32, 1, dtype=torch.float32, device=DEV)
+    bsi_ops.pack_queries_into(x, q8, sc, 2)
+    out_q8 = torch.full((32, 256), 99, dtype=torch.int8, device=DEV)
+    out_sc = torch.full((32, 1), -1.0, dtype=torch.float32, device=DEV)
+    bsi_ops.linear_from_packed_requant(q8, sc, cap, None, 2, torch.float16, False, [out_q8.data_ptr()], 256,
+                                       [out_sc.data_ptr()], 1)
+    assert bsi_ops.device_status() == 48
+    assert bsi_ops.device_status() == 0          # reading clears it
+    assert not out_q8.any()
