@@ -423,6 +423,25 @@ def run_opt(args, rank, world, local_rank):
         barrier()
         sampler.stop()
         e2e_ms = e0.elapsed_time(e1)
+    if args.kernel_split:
+        # device time per kernel over three more steps (CUPTI records through torch.profiler; informational,
+        # printed to stderr by rank 0, outside every timed region)
+        import collections
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        with torch.no_grad(), profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(3):
+                model.next_token(ids)
+            torch.cuda.synchronize()
+        if rank == 0:
+            per = collections.defaultdict(list)
+            for e in prof.events():
+                if e.device_type == torch.autograd.DeviceType.CUDA:
+                    per[e.name[:72]].append(e.device_time)
+            print("kernel | launches/step | ms/step | median us | max us", file=sys.stderr)
+            for name, v in sorted(per.items(), key=lambda kv: -sum(kv[1]))[:14]:
+                v = sorted(v)
+                print(f"{name} | {len(v) / 3:.0f} | {sum(v) / 3e3:.3f} | {v[len(v) // 2]:.1f} | {v[-1]:.1f}", file=sys.stderr)
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -469,6 +488,8 @@ def main():
     ap.add_argument("--opt-impl", default="tp", choices=["tp", "layers"],
                     help="OPT workloads: tensor-parallel decoder (default) or one BSIQuantizedLinear per nn.Linear")
     ap.add_argument("--cuda-graph", type=int, default=1, help="tensor-parallel OPT: replay the decoder stack from a CUDA graph")
+    ap.add_argument("--kernel-split", action="store_true",
+                    help="OPT workloads: after the timed regions, print the device time per kernel of three steps to stderr")
     ap.add_argument("--push", default="store", choices=["copy", "store"],
                     help="peer exchange: int8 blocks pushed by copy engines, or stored to every rank by the pack kernel")
     ap.add_argument("--microbatches", type=int, default=2, help="peer exchange: sequence groups run on streams of their own")

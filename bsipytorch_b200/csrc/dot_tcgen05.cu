@@ -24,6 +24,7 @@
 // word, raises a CTA-wide abort flag, every role leaves its loop, outstanding copies and MMAs
 // are waited for (bounded again), TMEM is freed and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -429,6 +430,16 @@ int launch_tile(const CUtensorMap& ma, const CUtensorMap& mb, const float* qs, i
     return check_launch("dot_i8 tcgen05 launch");
 }
 
+// BSI_B200_PDL=0 switches programmatic dependent launch off (read once).
+bool pdl_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("BSI_B200_PDL");
+        cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return cached == 1;
+}
+
 template <int BN, bool DBG, typename OutT, bool REQ = false>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
                 const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
@@ -442,16 +453,19 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     const int tiles_n = (R + BN - 1) / BN;
     const int tiles_total = tiles_m * tiles_n;
     cudaLaunchConfig_t cfg = {};
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: this kernel's set-up may overlap the tail of the kernel before it
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.blockDim = dim3(pair::kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = stream;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
     int resident = 0;
     if (dev >= 0 && dev < 64) resident = max_clusters[dev];
     if (resident == 0) {

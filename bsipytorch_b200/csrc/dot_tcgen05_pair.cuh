@@ -198,6 +198,9 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     uint16_t* xchg_vals = reinterpret_cast<uint16_t*>(tmem_slot + 4);                       // [2][kEpiWarps][32]
     volatile uint32_t* xchg_count = reinterpret_cast<volatile uint32_t*>(xchg_vals + 2 * kEpiWarps * 32);   // [kEpiWarps]
 
+    // let the next kernel of the stream start its own set-up as soon as every CTA of this grid is running
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t bar_base = smem_u32(bars);
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -253,6 +256,11 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+
+    // Programmatic dependent launch: everything above (barriers, TMEM, tensor-map prefetch) touched no global
+    // memory of an earlier kernel and may run while that kernel drains; from here on its results are needed.
+    // Without the launch attribute both instructions do nothing.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp < kFirstEpiWarp) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLow));
