@@ -1,6 +1,8 @@
 // Status strings, thread-local error text and device queries of the bsi_b200 library.
 #include "common.cuh"
 
+#include <stdlib.h>
+
 #include <stdarg.h>
 
 namespace bsi {
@@ -20,6 +22,15 @@ static int g_pack_block_cap = 0;
 
 int dot_sm_cap() { return g_dot_sm_cap; }
 int pack_block_cap() { return g_pack_block_cap; }
+
+bool pdl_enabled() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("BSI_B200_PDL");
+        cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return cached == 1;
+}
 
 int sm_count() {
     static int cached[64] = {0};

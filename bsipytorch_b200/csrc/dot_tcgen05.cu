@@ -430,16 +430,6 @@ int launch_tile(const CUtensorMap& ma, const CUtensorMap& mb, const float* qs, i
     return check_launch("dot_i8 tcgen05 launch");
 }
 
-// BSI_B200_PDL=0 switches programmatic dependent launch off (read once).
-bool pdl_enabled() {
-    static int cached = -1;
-    if (cached < 0) {
-        const char* e = getenv("BSI_B200_PDL");
-        cached = (e != nullptr && e[0] == '0') ? 0 : 1;
-    }
-    return cached == 1;
-}
-
 template <int BN, bool DBG, typename OutT, bool REQ = false>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
                 const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
