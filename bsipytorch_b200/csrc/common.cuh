@@ -65,23 +65,9 @@ struct RequantDst {
     float* scales[BSI_B200_MAX_PEERS];   // already offset to this linear's first output chunk
 };
 
-// True unless BSI_B200_PDL=0: kernels that follow one another on a stream are launched with programmatic
-// stream serialisation (their set-up may overlap the tail of the kernel before them).
+// True unless BSI_B200_PDL=0: the dot kernels are launched with programmatic stream serialisation (their set-up
+// may overlap the tail of a dot kernel right before them on the stream).
 bool pdl_enabled();
-
-// Launch configuration with the programmatic-serialisation attribute when enabled; `attr` must outlive the launch.
-inline cudaLaunchConfig_t pdl_config(dim3 grid, dim3 block, size_t smem, cudaStream_t stream, cudaLaunchAttribute* attr) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    return cfg;
-}
 
 // Reads and clears the status word of the peer barrier kernels (0 = clean, 64 + p = gave up waiting for rank p).
 int take_peer_status(int* v);

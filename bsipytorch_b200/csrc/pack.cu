@@ -467,9 +467,6 @@ template <typename T>
 __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_multi_kernel(
     const T* __restrict__ x, uint32_t total, uint32_t chunks, uint32_t ldx, uint32_t ld8, uint32_t scale_ld,
     double dec_scale, uint32_t dec_mult, uint32_t fast_limit, int bits, const MultiDst dst) {
-    // programmatic dependent launch: let the next kernel set itself up; wait for the producer of x
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const uint32_t stride = gridDim.x * 8u;
     const uint32_t first = blockIdx.x * 8u + (threadIdx.x >> 5);
@@ -820,13 +817,10 @@ extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t ro
         int64_t blocks = (rows * chunks + 7) / 8;                                                           \
         blocks = blocks < resident ? blocks : resident;                                                     \
         if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();                   \
-        cudaLaunchAttribute attr[1];                                                                        \
-        cudaLaunchConfig_t cfg = pdl_config(dim3(static_cast<unsigned>(blocks)), dim3(256), 0, stream, attr); \
-        BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, quantize_pack_multi_kernel<T>, static_cast<const T*>(x),      \
-                                        static_cast<uint32_t>(rows * chunks), static_cast<uint32_t>(chunks), \
-                                        static_cast<uint32_t>(ldx), static_cast<uint32_t>(ld8),             \
-                                        static_cast<uint32_t>(scale_ld), dec_scale, dec_mult,               \
-                                        static_cast<uint32_t>(LIMIT), bits, dst));                          \
+        quantize_pack_multi_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                   \
+            static_cast<const T*>(x), static_cast<uint32_t>(rows * chunks), static_cast<uint32_t>(chunks),  \
+            static_cast<uint32_t>(ldx), static_cast<uint32_t>(ld8), static_cast<uint32_t>(scale_ld), dec_scale, \
+            dec_mult, LIMIT, bits, dst);                                                                    \
     } while (0)
     if (dtype == BSI_DTYPE_F32) BSI_LAUNCH_MULTI(float, 127u);
     else if (dtype == BSI_DTYPE_F16) BSI_LAUNCH_MULTI(__half, 1000u);

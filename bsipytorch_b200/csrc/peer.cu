@@ -47,10 +47,9 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 // timeout_ns, records status 64 + p and returns: a missing rank must not hang the GPU.
 __global__ void peer_barrier_kernel(FlagTable t, int rank, int n, unsigned long long timeout_ns) {
     __shared__ uint32_t epoch_s;
-    // programmatic dependent launch: the next kernel may start its set-up now; this one needs every write of
-    // the kernels before it (they are what the barrier publishes)
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // Deliberately a plain launch, without programmatic dependent launch: a dependent kernel that becomes
+    // resident early holds its SMs while this kernel waits for other GPUs, and with two streams per rank the
+    // ranks can then starve each other's producers (seen as barrier timeouts, status 64 + rank).
     uint32_t* own = t.flags[rank];
     if (threadIdx.x == 0) {
         epoch_s = own[n] + 1u;
@@ -134,10 +133,8 @@ extern "C" int bsi_b200_peer_barrier(uint32_t* const* flags, int rank, int n, in
         t.flags[i] = flags[i];
     }
     if (int rc = require_sm100()) return rc;
-    cudaLaunchAttribute attr[1];
-    cudaLaunchConfig_t cfg = pdl_config(dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream_), attr);
-    BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, peer_barrier_kernel, t, rank, n,
-                                    static_cast<unsigned long long>(timeout_ms) * 1000000ull));
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+        t, rank, n, static_cast<unsigned long long>(timeout_ms) * 1000000ull);
     return check_launch("peer_barrier launch");
 }
 
