@@ -730,6 +730,39 @@ void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::caps
                  "bsi_b200_linear_i8_requant");
 }
 
+// Residual add + LayerNorm + activation pack (16-bit layer types). Returns x + delta (delta optional); the
+// packed LayerNorm output goes to the raw destinations as in pack_queries_multi.
+at::Tensor add_layernorm_pack(torch::Tensor x, c10::optional<torch::Tensor> delta, torch::Tensor weight, torch::Tensor bias,
+                              double eps, std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
+                              int64_t scale_ld, int decimalPlaces) {
+    TORCH_CHECK(x.dim() == 2 && x.is_cuda() && x.is_contiguous(), "x must be a contiguous 2D CUDA tensor");
+    TORCH_CHECK(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "x must be float16 or bfloat16");
+    TORCH_CHECK(weight.scalar_type() == x.scalar_type() && bias.scalar_type() == x.scalar_type() && weight.is_contiguous() &&
+                    bias.is_contiguous() && weight.numel() == x.size(1) && bias.numel() == x.size(1),
+                "LayerNorm weight / bias must match x");
+    TORCH_CHECK(!q8_ptrs.empty() && !scale_ptrs.empty(), "destination lists must not be empty");
+    check_clip();
+    TORCH_CHECK(chunk_scale_enabled(), "add_layernorm_pack needs BSI_FIXED_CHUNK_SCALE=1");
+    const void* dptr = nullptr;
+    at::Tensor d;
+    if (delta.has_value() && delta->defined()) {
+        d = delta->contiguous();
+        TORCH_CHECK(d.sizes() == x.sizes() && d.scalar_type() == x.scalar_type(), "delta must match x");
+        dptr = d.data_ptr();
+    }
+    at::Tensor out = dptr != nullptr ? at::empty_like(x) : x;
+    std::vector<int8_t*> q;
+    std::vector<float*> sc;
+    for (int64_t p : q8_ptrs) q.push_back(reinterpret_cast<int8_t*>(static_cast<intptr_t>(p)));
+    for (int64_t p : scale_ptrs) sc.push_back(reinterpret_cast<float*>(static_cast<intptr_t>(p)));
+    check_status(bsi_b200_add_layernorm_pack(x.data_ptr(), dptr, weight.data_ptr(), bias.data_ptr(), static_cast<float>(eps),
+                                             dtype_code(x), x.size(0), x.size(1), out.data_ptr(), decimalPlaces,
+                                             bits_queries(), static_cast<int>(q.size()), q.data(), ld8,
+                                             static_cast<int>(sc.size()), sc.data(), scale_ld, current_stream()),
+                 "bsi_b200_add_layernorm_pack");
+    return out;
+}
+
 py::dict debug_batch(const PackedBatch& b) {
     py::dict d;
     d["words"] = b.words;
@@ -836,6 +869,8 @@ PYBIND11_MODULE(bsi_ops, m) {
     m.def("linear_from_packed_requant", &linear_from_packed_requant, py::arg("q8"), py::arg("scales"),
           py::arg("keyset_cuda_cap"), py::arg("bias"), py::arg("decimal_places"), py::arg("layer_dtype"), py::arg("relu"),
           py::arg("q8_ptrs"), py::arg("ld8"), py::arg("scale_ptrs"), py::arg("scale_ld"));
+    m.def("add_layernorm_pack", &add_layernorm_pack, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("bias"),
+          py::arg("eps"), py::arg("q8_ptrs"), py::arg("ld8"), py::arg("scale_ptrs"), py::arg("scale_ld"), py::arg("decimal_places"));
     m.def("peer_copy_2d", &peer_copy_2d, py::arg("dst"), py::arg("dst_pitch"), py::arg("src"), py::arg("src_pitch"),
           py::arg("width_bytes"), py::arg("height"));
     m.def("pack_queries_multi", &pack_queries_multi, py::arg("x2d"), py::arg("q8_ptrs"), py::arg("ld8"),

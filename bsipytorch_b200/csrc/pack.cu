@@ -522,6 +522,115 @@ __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_multi_
     }
 }
 
+// Residual add + LayerNorm + activation pack of one token row per block, for 16-bit layer types:
+//   x_out = T(x + delta)                      (delta may be null: x_out = x)
+//   y     = T((x_out - mean) * rstd * gamma + beta), float32 statistics over the row (two passes over registers)
+//   y is quantised per 256-element chunk exactly as the chunk-mode packer would quantise it and the int8
+//   image / chunk scales go to the destinations (own buffer or peer mappings), as in the multi-destination pack.
+// Warp w owns chunks w, w + 8, ...; lane L the 8 consecutive elements 8L..8L+7 of each (the packer's mapping), so the
+// row stays in registers between the add, the statistics and the quantisation. CPW = chunks per warp (H <= 2048*CPW).
+template <typename T, int CPW>
+__global__ void __launch_bounds__(256) add_layernorm_pack_kernel(
+    const T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ gamma, const T* __restrict__ beta,
+    float eps, int rows, int H, int chunks, T* __restrict__ x_out, double dec_scale, uint32_t dec_mult,
+    uint32_t fast_limit, int bits, int64_t ld8, int64_t scale_ld, const MultiDst dst) {
+    __shared__ float red[2][8];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const bool try_fast = dec_mult != 0u && dec_mult <= fast_limit;
+    const float inv_h = 1.0f / static_cast<float>(H);
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int64_t base = static_cast<int64_t>(row) * H;
+        float v[CPW][8];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < CPW; ++i) {
+            const int c = warp + i * 8;
+            if (c < chunks) {
+                const int64_t off = base + c * 256 + lane * 8;
+                uint4 raw = __ldg(reinterpret_cast<const uint4*>(x + off));
+                const T* xv = reinterpret_cast<const T*>(&raw);
+                if (delta != nullptr) {
+                    const uint4 draw = __ldg(reinterpret_cast<const uint4*>(delta + off));
+                    const T* dv = reinterpret_cast<const T*>(&draw);
+                    T ov[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        ov[e] = static_cast<T>(to_float(xv[e]) + to_float(dv[e]));
+                        v[i][e] = to_float(ov[e]);
+                    }
+                    *reinterpret_cast<uint4*>(x_out + off) = *reinterpret_cast<const uint4*>(ov);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[i][e] = to_float(xv[e]);
+                    if (x_out != x) *reinterpret_cast<uint4*>(x_out + off) = raw;
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sum += v[i][e];
+            }
+        }
+        // mean
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) red[0][warp] = sum;
+        __syncthreads();
+        float tot = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tot += red[0][w];
+        const float mean = tot * inv_h;
+        // variance around the mean
+        float sq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < CPW; ++i) {
+            if (warp + i * 8 < chunks) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float d = v[i][e] - mean;
+                    sq = fmaf(d, d, sq);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) red[1][warp] = sq;
+        __syncthreads();
+        float tsq = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) tsq += red[1][w];
+        const float rstd = rsqrtf(tsq * inv_h + eps);
+        // normalise, round to the layer type, quantise the chunk, store everywhere
+#pragma unroll
+        for (int i = 0; i < CPW; ++i) {
+            const int c = warp + i * 8;
+            if (c < chunks) {
+                const int col = c * 256 + lane * 8;
+                const uint4 graw = __ldg(reinterpret_cast<const uint4*>(gamma + col));
+                const uint4 braw = __ldg(reinterpret_cast<const uint4*>(beta + col));
+                const T* gv = reinterpret_cast<const T*>(&graw);
+                const T* bv = reinterpret_cast<const T*>(&braw);
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+                    f[e] = to_float(static_cast<T>(fmaf((v[i][e] - mean) * rstd, to_float(gv[e]), to_float(bv[e]))));
+                int shift;
+                u64 packed;
+                if (!(try_fast && fast_quantise<T>(f, dec_mult, bits, shift, packed)))
+                    generic_quantise(f[0], f[1], f[2], f[3], f[4], f[5], f[6], f[7], dec_scale, dec_mult, bits, &shift,
+                                     &packed);
+                const int64_t q8_off = static_cast<int64_t>(row) * ld8 + col;
+                const int64_t sc_off = static_cast<int64_t>(row) * scale_ld + c;
+                const float scale = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);
+#pragma unroll
+                for (int d = 0; d < BSI_B200_MAX_PEERS; ++d) {
+                    if (d < dst.n_q8) *reinterpret_cast<u64*>(dst.q8[d] + q8_off) = packed;
+                    if (d < dst.n_scales && lane == 0) dst.scales[d][sc_off] = scale;
+                }
+            }
+        }
+        __syncthreads();   // red[] is rewritten by the next row
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
     const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
@@ -827,6 +936,72 @@ extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t ro
     else BSI_LAUNCH_MULTI(__nv_bfloat16, 1000u);
 #undef BSI_LAUNCH_MULTI
     return check_launch("quantize_pack_multi launch");
+}
+
+extern "C" int bsi_b200_add_layernorm_pack(const void* x, const void* delta, const void* gamma, const void* beta,
+                                           float eps, int dtype, int64_t rows, int64_t H, void* x_out,
+                                           int decimal_places, int bits, int n_q8_dst, int8_t* const* q8_dst,
+                                           int64_t ld8, int n_scale_dst, float* const* scale_dst, int64_t scale_ld,
+                                           bsi_stream_t stream_) {
+    using namespace bsi;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (rows < 0 || H <= 0) return fail(BSI_ERR_INVALID, "add_layernorm_pack: bad rows/H");
+    if (dtype != BSI_DTYPE_F16 && dtype != BSI_DTYPE_BF16)
+        return fail(BSI_ERR_UNSUPPORTED, "add_layernorm_pack: the layer type must be float16 or bfloat16");
+    if ((H & 255) != 0 || H > 16384) return fail(BSI_ERR_UNSUPPORTED, "add_layernorm_pack: H must be a multiple of 256, at most 16384");
+    if (bits < 2 || bits > 8) return fail(BSI_ERR_UNSUPPORTED, "add_layernorm_pack: bits must be in [2, 8]");
+    if (rows == 0) return BSI_OK;
+    if (rows > 0x7fffffffll) return fail(BSI_ERR_UNSUPPORTED, "add_layernorm_pack: too many rows");
+    if (x == nullptr || gamma == nullptr || beta == nullptr || x_out == nullptr || q8_dst == nullptr || scale_dst == nullptr)
+        return fail(BSI_ERR_INVALID, "add_layernorm_pack: null pointer");
+    auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+    if (misaligned(x) || misaligned(x_out) || misaligned(gamma) || misaligned(beta) || (delta != nullptr && misaligned(delta)))
+        return fail(BSI_ERR_INVALID, "add_layernorm_pack: pointers must be 16-byte aligned");
+    const int64_t chunks = H / 256;
+    if (n_q8_dst < 1 || n_q8_dst > BSI_B200_MAX_PEERS || n_scale_dst < 1 || n_scale_dst > BSI_B200_MAX_PEERS ||
+        ld8 < H || (ld8 & 7) != 0 || scale_ld < chunks)
+        return fail(BSI_ERR_INVALID, "add_layernorm_pack: bad destinations (ld8 >= H, ld8 % 8 == 0, scale_ld >= H/256)");
+    MultiDst dst = {};
+    dst.n_q8 = n_q8_dst;
+    dst.n_scales = n_scale_dst;
+    for (int i = 0; i < n_q8_dst; ++i) {
+        if (q8_dst[i] == nullptr || (reinterpret_cast<uintptr_t>(q8_dst[i]) & 7) != 0)
+            return fail(BSI_ERR_INVALID, "add_layernorm_pack: q8 destinations must be non-null and 8-byte aligned");
+        dst.q8[i] = q8_dst[i];
+    }
+    for (int i = 0; i < n_scale_dst; ++i) {
+        if (scale_dst[i] == nullptr) return fail(BSI_ERR_INVALID, "add_layernorm_pack: null scale destination");
+        dst.scales[i] = scale_dst[i];
+    }
+    if (int rc = require_sm100()) return rc;
+    const double dec_scale = pow(10.0, static_cast<double>(decimal_places));
+    uint32_t dec_mult = 0;
+    if (decimal_places >= 0 && decimal_places <= 8) {
+        dec_mult = 1;
+        for (int i = 0; i < decimal_places; ++i) dec_mult *= 10u;
+    }
+    const int cpw = static_cast<int>((chunks + 7) / 8);   // chunks per warp, 8 warps
+    int64_t blocks = rows;
+    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();
+#define BSI_LAUNCH_ALP(T, CPW_)                                                                                   \
+    add_layernorm_pack_kernel<T, CPW_><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                       \
+        static_cast<const T*>(x), static_cast<const T*>(delta), static_cast<const T*>(gamma),                    \
+        static_cast<const T*>(beta), eps, static_cast<int>(rows), static_cast<int>(H), static_cast<int>(chunks), \
+        static_cast<T*>(x_out), dec_scale, dec_mult, 1000u, bits, ld8, scale_ld, dst)
+#define BSI_LAUNCH_ALP_T(T)                       \
+    do {                                          \
+        if (cpw <= 1) BSI_LAUNCH_ALP(T, 1);       \
+        else if (cpw <= 2) BSI_LAUNCH_ALP(T, 2);  \
+        else if (cpw <= 4) BSI_LAUNCH_ALP(T, 4);  \
+        else BSI_LAUNCH_ALP(T, 8);                \
+    } while (0)
+    if (dtype == BSI_DTYPE_F16) BSI_LAUNCH_ALP_T(__half);
+    else BSI_LAUNCH_ALP_T(__nv_bfloat16);
+#undef BSI_LAUNCH_ALP_T
+#undef BSI_LAUNCH_ALP
+    return check_launch("add_layernorm_pack launch");
 }
 
 extern "C" int bsi_b200_recombine_i8(const uint64_t* words, int64_t rows, int bits, int64_t W,

@@ -61,6 +61,10 @@ class BsiDeviceOps:
     def linear(self, q8, scales, keys, bias, out_dtype, relu=False):
         return self.m.linear_from_packed(q8, scales, keys, bias, self.dp, out_dtype, relu)
 
+    def add_ln_pack(self, x, delta, ln, q8_ptrs, ld8, scale_ptrs, scale_ld):
+        """x + delta (delta may be None), LayerNorm `ln` of the sum, packed to the given addresses; returns the sum."""
+        return self.m.add_layernorm_pack(x, delta, ln.weight, ln.bias, ln.eps, q8_ptrs, ld8, scale_ptrs, scale_ld, self.dp)
+
     def linear_requant(self, q8, scales, keys, bias, layer_dtype, relu, q8_ptrs, ld8, scale_ptrs, scale_ld):
         """Linear whose output is re-quantised for the next linear inside its epilogue and stored to the given
         addresses (needs a 16-bit layer type and a multiple of 256 output features)."""
@@ -172,6 +176,9 @@ class TPDecoderLayer(nn.Module):
         # fc1 -> ReLU -> re-quantise inside the fc1 epilogue: CUDA extension, 16-bit layer type, whole chunks per rank
         self.fuse_requant = (isinstance(ops, BsiDeviceOps) and dtype in (torch.float16, torch.bfloat16)
                              and (self.f_hi - self.f_lo) % 256 == 0 and ops.dp <= 3)
+        # residual add + LayerNorm + pack in one kernel: CUDA extension, 16-bit layer type
+        self.fuse_ln = (isinstance(ops, BsiDeviceOps) and dtype in (torch.float16, torch.bfloat16)
+                        and H % 256 == 0 and H <= 16384)
         self.self_attn_layer_norm = nn.LayerNorm(H, device=device, dtype=dtype)
         self.final_layer_norm = nn.LayerNorm(H, device=device, dtype=dtype)
         self.keys_qkv = self.keys_out = self.keys_fc1 = self.keys_fc2 = None
@@ -246,30 +253,39 @@ class TPDecoderLayer(nn.Module):
         attn = F.scaled_dot_product_attention(q, k, v, is_causal=True)               # [B, nh, T, hd]
         return attn.transpose(1, 2).reshape(B * T, Hl)
 
-    def forward_peer(self, x_loc, B, T, px: "PeerExchange"):
-        """The layer with stores into peer buffers in place of collectives (see PeerExchange)."""
+    def forward_peer(self, x_loc, delta, B, T, px: "PeerExchange"):
+        """The layer with stores into peer buffers in place of collectives (see PeerExchange). `delta` is the
+        previous layer's fc2 output for the own tokens, still to be added to the residual stream (None at the
+        first layer); returns (x, delta) in the same form."""
         ops, dt, m, g = self.ops, self.dtype, self.ops.m, self.rank
         H, Fd, Qn = self.cfg.hidden_size, self.cfg.ffn_dim, px.Qn
         Hl, Fl = self.h_hi - self.h_lo, self.f_hi - self.f_lo
         hc, fc = H // 256, Fd // 256
+        order = [(g + 1 + k) % self.world for k in range(self.world)]   # every rank starts with its successor
 
-        def rows_to_all(h):      # own tokens -> rows [g*Qn, (g+1)*Qn) of R on every rank
-            px.pack_to_all(h, ops.dp, "R_q8", "R_sc", g * Qn * H, g * Qn * hc * 4, H, hc, Qn)
+        def ln_rows_to_all(x, d, ln):   # x + d, LayerNorm, pack: own tokens -> rows [g*Qn, (g+1)*Qn) of R on every rank
+            if self.fuse_ln:
+                q8p, scp = px.ptrs("R_q8", g * Qn * H), px.ptrs("R_sc", g * Qn * hc * 4)
+                x = ops.add_ln_pack(x, d, ln, [q8p[r] for r in order], H, [scp[r] for r in order], hc)
+                px.barrier()
+                return x
+            if d is not None:
+                x = x + d
+            px.pack_to_all(ln(x), ops.dp, "R_q8", "R_sc", g * Qn * H, g * Qn * hc * 4, H, hc, Qn)
+            return x
 
         def to_owner(q8, sc, keys, bias):   # [Q, H/G] output block -> column block g of T on each token's owner
             m.linear_from_packed_scatter(q8, sc, keys, bias, ops.dp, dt, False, px.ptrs("T", g * Hl * px.esz), Qn, H)
             px.barrier()
 
-        rows_to_all(self.self_attn_layer_norm(x_loc))
+        x_loc = ln_rows_to_all(x_loc, delta, self.self_attn_layer_norm)
         qkv = ops.linear(px.R_q8, px.R_sc, self.keys_qkv, self.bias_qkv, dt)          # [Q, 3 * H/G]
         attn = self._attention(qkv, B, T)
         px.pack_to_all(attn, ops.dp, "C1_q8", "C1_sc", g * Hl, g * (Hl // 256) * 4, H, hc, px.Q)
         to_owner(px.C1_q8, px.C1_sc, self.keys_out, self.bias_out)
-        x_loc = x_loc + px.T
-        rows_to_all(self.final_layer_norm(x_loc))
+        x_loc = ln_rows_to_all(x_loc, px.T, self.final_layer_norm)
         if self.fuse_requant:
             # fc1 -> ReLU -> re-quantise in the fc1 epilogue, stored into C2 of every rank while the dot runs
-            order = [(g + 1 + k) % self.world for k in range(self.world)]
             q8p, scp = px.ptrs("C2_q8", g * Fl), px.ptrs("C2_sc", g * (Fl // 256) * 4)
             ops.linear_requant(px.R_q8, px.R_sc, self.keys_fc1, self.bias_fc1, dt, True, [q8p[r] for r in order], Fd,
                                [scp[r] for r in order], fc)
@@ -278,22 +294,34 @@ class TPDecoderLayer(nn.Module):
             f = ops.linear(px.R_q8, px.R_sc, self.keys_fc1, self.bias_fc1, dt, relu=True)  # [Q, F/G]
             px.pack_to_all(f, ops.dp, "C2_q8", "C2_sc", g * Fl, g * (Fl // 256) * 4, Fd, fc, px.Q)
         to_owner(px.C2_q8, px.C2_sc, self.keys_fc2, self.bias_fc2)
-        return x_loc + px.T
+        return x_loc, px.T
 
-    def forward(self, x_loc, B, T, px=None):
+    def forward(self, x_loc, delta, B, T, px=None):
+        """(x, delta) -> (x, delta): `delta` is the fc2 output of the previous layer for the own tokens, not yet
+        added to the residual stream `x` (None at the first layer)."""
         if px is not None:
-            return self.forward_peer(x_loc, B, T, px)
+            return self.forward_peer(x_loc, delta, B, T, px)
         Q = B * T
         ops, dt = self.ops, self.dtype
-        h = self.self_attn_layer_norm(x_loc)
-        q8, sc = self._pack_gather_rows(h, Q)
+        H = self.cfg.hidden_size
+
+        def ln_pack(x, d, ln):
+            if self.fuse_ln and self.world == 1:
+                q8 = torch.empty(Q, H, dtype=torch.int8, device=x.device)
+                sc = torch.empty(Q, H // 256, dtype=torch.float32, device=x.device)
+                x = ops.add_ln_pack(x, d, ln, [q8.data_ptr()], H, [sc.data_ptr()], H // 256)
+                return x, q8, sc
+            if d is not None:
+                x = x + d
+            q8, sc = self._pack_gather_rows(ln(x), Q)
+            return x, q8, sc
+
+        x_loc, q8, sc = ln_pack(x_loc, delta, self.self_attn_layer_norm)
         qkv = ops.linear(q8, sc, self.keys_qkv, self.bias_qkv, dt)                   # [Q, 3 * H/G]
         attn = self._attention(qkv, B, T)
         q8, sc = self._pack_gather_cols(attn)
         o = ops.linear(q8, sc, self.keys_out, self.bias_out, dt)                      # [Q, H/G]
-        x_loc = x_loc + self._to_token_shard(o)
-        h = self.final_layer_norm(x_loc)
-        q8, sc = self._pack_gather_rows(h, Q)
+        x_loc, q8, sc = ln_pack(x_loc, self._to_token_shard(o), self.final_layer_norm)
         if self.fuse_requant and self.world == 1:
             Fd = self.cfg.ffn_dim
             q8f = torch.empty(Q, Fd, dtype=torch.int8, device=x_loc.device)
@@ -304,7 +332,7 @@ class TPDecoderLayer(nn.Module):
             f = ops.linear(q8, sc, self.keys_fc1, self.bias_fc1, dt, relu=True)       # [Q, F/G]
             q8, sc = self._pack_gather_cols(f)
         o = ops.linear(q8, sc, self.keys_fc2, self.bias_fc2, dt)                      # [Q, H/G]
-        return x_loc + self._to_token_shard(o)
+        return x_loc, self._to_token_shard(o)
 
 
 class TPOPTForCausalLM(nn.Module):
@@ -336,10 +364,10 @@ class TPOPTForCausalLM(nn.Module):
         Qn = Q // G
         ids = input_ids.reshape(Q)[self.rank * Qn:(self.rank + 1) * Qn]
         pos = torch.arange(self.rank * Qn, (self.rank + 1) * Qn, device=input_ids.device) % T + 2   # OPT's offset
-        x = self.embed_tokens(ids) + self.embed_positions(pos)
+        x, delta = self.embed_tokens(ids) + self.embed_positions(pos), None
         for layer in self.layers:
-            x = layer(x, b, T, px)
-        return self.final_layer_norm(x)
+            x, delta = layer(x, delta, b, T, px)
+        return self.final_layer_norm(x + delta)
 
     def _micro(self, B, T):
         """Number of micro-batches for a [B, T] input: with peer exchange the batch is split into groups of
@@ -373,7 +401,7 @@ class TPOPTForCausalLM(nn.Module):
         for m in range(M):
             self._streams[m].wait_stream(cur)
         # layer by layer, alternating between the micro-batches, so that the host enqueues them interleaved
-        xs = []
+        xs, deltas = [], [None] * M
         for m in range(M):
             with torch.cuda.stream(self._streams[m]):
                 ids_m = input_ids[m * b:(m + 1) * b]
@@ -384,10 +412,10 @@ class TPOPTForCausalLM(nn.Module):
         for layer in self.layers:
             for m in range(M):
                 with torch.cuda.stream(self._streams[m]):
-                    xs[m] = layer(xs[m], b, T, pxs[m])
+                    xs[m], deltas[m] = layer(xs[m], deltas[m], b, T, pxs[m])
         for m in range(M):
             with torch.cuda.stream(self._streams[m]):
-                out = self.final_layer_norm(xs[m])
+                out = self.final_layer_norm(xs[m] + deltas[m])
                 out.record_stream(cur)
                 outs.append(out)
         for m in range(M):

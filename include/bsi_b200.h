@@ -187,6 +187,20 @@ int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t rows, int64_t
                                  int64_t ld8, int n_scale_dst, float* const* scale_dst, int64_t scale_ld,
                                  bsi_stream_t stream);
 
+/* Residual add + LayerNorm + activation pack in one pass over a token block, for a 16-bit layer type
+ * (dtype BSI_DTYPE_F16 / BF16; x, delta, gamma, beta and x_out all of that type, rows contiguous, H
+ * elements each): x_out = x + delta (delta may be NULL; x_out may be x), y = LayerNorm(x_out) with float32
+ * statistics, rounded to the layer type, then quantised per 256-element chunk exactly as
+ * bsi_b200_quantize_pack (chunk mode) quantises it; the int8 image and chunk scales go to the
+ * destinations as in bsi_b200_quantize_pack_multi. Replaces, in the OPT decoder layer, the residual add,
+ * the LayerNorm and the packer of the following BSI linears (three passes over the hidden states in the
+ * reference's flow: two torch kernels, then the query builder). H % 256 == 0, H <= 16384. */
+int bsi_b200_add_layernorm_pack(const void* x, const void* delta, const void* gamma, const void* beta,
+                                float eps, int dtype, int64_t rows, int64_t H, void* x_out,
+                                int decimal_places, int bits, int n_q8_dst, int8_t* const* q8_dst,
+                                int64_t ld8, int n_scale_dst, float* const* scale_dst, int64_t scale_ld,
+                                bsi_stream_t stream);
+
 /* Copies a block of `height` rows of `width_bytes` bytes between device buffers (either may be a peer
  * mapping) with the copy engines, enqueued on `stream`: cudaMemcpy2DAsync, device to device. Used to
  * push a rank's block of packed activations to its peers without occupying SMs. */

@@ -83,12 +83,52 @@ def test_tensor_parallel_forward_on_one_rank_equals_the_per_linear_model():
         with torch.no_grad():
             want, got = ref(ids), tp(ids)
         assert torch.isfinite(got).all()
-        assert torch.equal(got, want)
-        assert torch.equal(tp.next_token(ids), ref.next_token(ids))
+        if dtype == torch.float32:
+            assert torch.equal(got, want)        # every fused piece is exact; LayerNorm stays torch's in float32
+            assert torch.equal(tp.next_token(ids), ref.next_token(ids))
+        else:
+            # 16-bit layer types run the library's own add + LayerNorm + pack kernel: same formula as torch's
+            # LayerNorm, float32 statistics in another summation order, so the last bit of an activation may differ
+            rel = float((got.float() - want.float()).norm() / want.float().norm())
+            assert rel < 2e-2, rel
+            assert (tp.next_token(ids) == ref.next_token(ids)).float().mean() >= 0.75
         tp.capture(4, 32)                                   # replayed from a CUDA graph: same values
-        assert torch.equal(tp(ids), want)
+        assert torch.equal(tp(ids), got)
         ids2 = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(9)).to(DEV)
-        assert torch.equal(tp(ids2), ref(ids2))
+        eager = build_opt_tp(cfg, dtype=dtype, device=DEV, seed=11)
+        assert torch.equal(tp(ids2), eager(ids2))
+
+
+def test_add_layernorm_pack_against_torch():
+    from bsipytorch_b200 import bsi_ops
+
+    g = torch.Generator().manual_seed(21)
+    for dtype, H, rows in [(torch.float16, 1024, 70), (torch.bfloat16, 768, 33), (torch.float16, 4096, 16)]:
+        x = torch.randn(rows, H, generator=g).to(dtype).to(DEV)
+        d = (0.3 * torch.randn(rows, H, generator=g)).to(dtype).to(DEV)
+        ln = torch.nn.LayerNorm(H, device=DEV, dtype=dtype)
+        with torch.no_grad():
+            ln.weight.copy_(1.0 + 0.1 * torch.randn(H, generator=g).to(DEV))
+            ln.bias.copy_(0.1 * torch.randn(H, generator=g).to(DEV))
+        q8 = torch.full((rows, H), 99, dtype=torch.int8, device=DEV)
+        sc = torch.full((rows, H // 256), -1.0, device=DEV)
+        out = bsi_ops.add_layernorm_pack(x, d, ln.weight, ln.bias, ln.eps, [q8.data_ptr()], H, [sc.data_ptr()], H // 256, 2)
+        assert torch.equal(out, x + d)                       # the residual sum is exact
+        with torch.no_grad():
+            y = ln(x + d)
+        want_q8 = torch.empty_like(q8)
+        want_sc = torch.empty_like(sc)
+        bsi_ops.pack_queries_into(y, want_q8, want_sc, 2)
+        # the library's LayerNorm may differ from torch's in the last bit of y: integers within one step, almost all equal
+        diff = (q8.int() - want_q8.int()).abs()
+        same_scale = (sc == want_sc)
+        assert same_scale.float().mean() > 0.98
+        mask = same_scale.repeat_interleave(256, dim=1)
+        assert int(diff[mask].max()) <= 1 and float((diff[mask] > 0).float().mean()) < 0.02
+        # no delta: x passes through untouched
+        out2 = bsi_ops.add_layernorm_pack(x, None, ln.weight, ln.bias, ln.eps, [q8.data_ptr()], H, [sc.data_ptr()], H // 256, 2)
+        assert out2.data_ptr() == x.data_ptr()
+    assert bsi_ops.device_status() == 0
 
 
 def test_linear_from_packed_relu_and_column_block_pack():
