@@ -378,7 +378,10 @@ def run_opt(args, rank, world, local_rank):
         graphed = bool(args.cuda_graph) and (world == 1 or model.exchange == "peer")
         if graphed:
             model.capture(spec["batch"], spec["seq"])
-        launches_per_layer = 8 if world == 1 else 14      # 4 activation packs + 4 fused linears (+ 6 flag barriers)
+        # this library's kernels per layer: 4 fused linears + the activation packs (two of them inside the add +
+        # LayerNorm + pack kernel; the fc2 one disappears when fc1 re-quantises in its epilogue) + 6 flag barriers
+        layer0 = model.layers[0]
+        launches_per_layer = 4 + (3 if layer0.fuse_requant else 4) + (6 if (world > 1 and model.exchange == "peer") else 0)
         scheme = ("tensor parallel: R-sharded BSI linears, head-sharded attention, token-sharded residual; packed int8 "
                   "activations and linear outputs " + ("stored straight into peer buffers over NVLink by the pack / linear kernels"
                                                        if model.exchange == "peer" else "moved by NCCL all-gather / all-to-all"))

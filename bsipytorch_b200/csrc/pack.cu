@@ -981,9 +981,7 @@ extern "C" int bsi_b200_add_layernorm_pack(const void* x, const void* delta, con
         for (int i = 0; i < decimal_places; ++i) dec_mult *= 10u;
     }
     const int cpw = static_cast<int>((chunks + 7) / 8);   // chunks per warp, 8 warps
-    int64_t blocks = rows;
-    const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
-    if (blocks > cap) blocks = cap;
+    int64_t blocks = rows;   // one block per row; the kernel's row loop only matters under a block cap
     if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();
 #define BSI_LAUNCH_ALP(T, CPW_)                                                                                   \
     add_layernorm_pack_kernel<T, CPW_><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                       \
