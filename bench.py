@@ -119,12 +119,23 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def host_threads():
+    """Threads the CPU arm uses: every core this process may run on (a launcher such as torchrun sets
+    OMP_NUM_THREADS=1 for its workers; the CPU baseline is meant to have all the host cores)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_port_rate(q, k, target_s, threads=0):
     """Times the CPU port on a bounded sample of query rows; returns (TOPS, rows, seconds, threads)."""
     from oracle import oracle as o
     keys = o.CpuKeyset(k.numpy(), 2)
     qn = q.float().numpy()
-    nthreads = o.num_threads() if threads <= 0 else threads
+    if threads <= 0:
+        threads = host_threads()
+    nthreads = threads
     rows = min(2 * nthreads, qn.shape[0])
     t0 = time.perf_counter()
     keys.dot(qn[:rows], threads)
@@ -151,21 +162,21 @@ def run_reference(args, wl, rank, world):
     q, k = make_inputs(wl)
     keys = o.CpuKeyset(k.numpy(), 2)
     qn = q.float().numpy()
-    nthreads = o.num_threads()
+    nthreads = host_threads()
     # each step is a bounded sample of the workload's query rows, sized so that the whole run
     # (warm-up + steps) stays around two minutes whatever K is
     per_step = min(5.0, 120.0 / max(1, args.steps + args.warmup))
     rows = min(2 * nthreads, qn.shape[0])
-    keys.dot(qn[:rows])                                  # first touch (page faults, thread start-up)
+    keys.dot(qn[:rows], nthreads)                                  # first touch (page faults, thread start-up)
     t0 = time.perf_counter()
-    keys.dot(qn[:rows])
+    keys.dot(qn[:rows], nthreads)
     t = time.perf_counter() - t0
     rows = int(min(qn.shape[0], max(1, rows * per_step / max(t, 1e-6))))
     for _ in range(args.warmup):
-        keys.dot(qn[:rows])
+        keys.dot(qn[:rows], nthreads)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        keys.dot(qn[:rows])
+        keys.dot(qn[:rows], nthreads)
     t = time.perf_counter() - t0
     ops = 2.0 * rows * wl["R"] * wl["D"] * args.steps
     tops = ops / t / 1e12
