@@ -1,20 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the BSI tensor-dot hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload fc1|fc2] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-One step = one pass of the hot path over one batch: the fixed76 chunk-scale BSI dot of the named
-workload (FC1-like: Q=512 fp16 activations x R=8192 keys x D=2048; FC2-like: Q=512 x R=2048 x D=8192),
-keys prebuilt, queries packed. ``value`` is effective TOPS = 2*Q*R*D / time with every operand resident
-in HBM; ``e2e`` is the same metric through the public ``bsi_ops`` entry points starting from pinned
-HOST activations and ending with the float32 result back on the host.
+Default workload (fc1): one step = one pass of the hot path over one batch, the fixed76 chunk-scale BSI dot of
+the FC1-like shape (Q=512 fp16 activations x R=8192 keys x D=2048; fc2: Q=512 x R=2048 x D=8192), keys prebuilt,
+queries packed. ``value`` is effective TOPS = 2*Q*R*D / time with every operand resident in HBM; ``e2e`` is the
+same metric through the public ``bsi_ops`` entry points starting from pinned HOST activations and ending with the
+float32 result back on the host.
 
-N > 1 (launched under torchrun, one rank per GPU): the keys are sharded along R, every rank owns an
-R-row shard of the same size (weak scaling) and there is no data-path collective in the dot itself;
-timing is the max over ranks.
+N > 1 (launched under torchrun, one rank per GPU): the keys are sharded along R, every rank owns an R-row shard
+of the same size (weak scaling) and there is no data-path collective in the dot itself; timing is the max over
+ranks.
 
-``--impl reference`` times the reference's CPU path (the bsiCPP-semantics port under oracle/) on the
-host cores, on a bounded sample of the same workload.
+Other workloads: ``pack`` / ``pack-lean`` / ``ewah`` time the HBM-bound kernels of the path (GB/s against the
+measured copy bandwidth); ``opt-125m`` / ``opt-6.7b`` time the OPT forward with every q/k/v/out/fc1/fc2 linear as
+a BSI op (tokens/s; N > 1: tensor parallel over R-sharded keys, strong scaling, see bsipytorch_b200/opt_tp.py).
+
+``--impl reference`` times the reference's CPU path (the bsiCPP-semantics port under oracle/) on the host cores,
+on a bounded sample of the same workload, and, where the reference's own kernels were compiled, those too.
 """
 import argparse
 import json
