@@ -176,6 +176,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, int32_t (&r)[32]) {
         : "memory");
 }
 
+// 16 columns into r[0..15] (the tail piece of tiles whose column count per warp is not a multiple of 32).
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 template <int BN, bool DBG>
@@ -474,21 +485,24 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
-// Pair kernel tile width: widest tile unless a narrower one fills more of the machine.
-int pick_bn_pair(int64_t Q, int64_t R) {
+// Pair kernel tile width. A CTA spends about (128 + BN / 2) * 256 bytes of operand delivery per chunk, at roughly
+// 50 bytes per clock from L2 into shared memory, which for every width outweighs the 4 * BN tensor-pipe clocks of
+// the chunk; a pair's time is that per chunk times the tiles it walks through. The widest tile wins unless a
+// narrower one needs fewer rounds over the pairs. float32 output may use any multiple of 32, the 16-bit layer
+// epilogues (whole 64-column store rounds) the powers of two.
+int pick_bn_pair(int64_t Q, int64_t R, bool any_width) {
     const int pairs = sm_count() / 2;
     const int64_t mt = (Q + 255) / 256;
-    const int cand[3] = {256, 128, 64};
-    const double eff[3] = {1.0, 0.85, 0.6};
     int best = 256;
     double best_cost = 1e300;
-    for (int i = 0; i < 3; ++i) {
-        const int64_t tiles = mt * ((R + cand[i] - 1) / cand[i]);
+    for (int bn = 256; bn >= 64; bn -= 32) {
+        if (!any_width && bn != 256 && bn != 128 && bn != 64) continue;
+        const int64_t tiles = mt * ((R + bn - 1) / bn);
         const int64_t waves = (tiles + pairs - 1) / pairs;
-        const double cost = static_cast<double>(waves) * cand[i] / eff[i];
+        const double cost = static_cast<double>(waves) * (655.0 + 2.56 * bn);
         if (cost < best_cost * 0.999) {
             best_cost = cost;
-            best = cand[i];
+            best = bn;
         }
     }
     return best;
@@ -539,8 +553,10 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     }
     if (Q > 0x7fffff00ll || R > 0x7fffff00ll || chunks > 0x400000)
         return fail(BSI_ERR_UNSUPPORTED, "dot_i8: Q, R or chunks too large");
-    const int bn = force_bn ? force_bn : pick_bn_pair(Q, R);
-    if (bn != 64 && bn != 128 && bn != 256) return fail(BSI_ERR_INVALID, "dot_i8: tile width must be 64, 128 or 256");
+    const bool any_width = y_dtype == BSI_DTYPE_F32;
+    const int bn = force_bn ? force_bn : pick_bn_pair(Q, R, any_width);
+    if (bn < 64 || bn > 256 || (bn & 31) != 0 || (!any_width && (bn & (bn - 1)) != 0))
+        return fail(BSI_ERR_INVALID, "dot_i8: tile width must be a multiple of 32 in [64, 256] (64, 128 or 256 for 16-bit outputs)");
     if (dbg_iacc != nullptr && y_dtype != BSI_DTYPE_F32)
         return fail(BSI_ERR_INVALID, "dot_i8: the accumulator dump is only available with float32 output");
     CUtensorMap ma, mb;
@@ -569,11 +585,19 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
         return launch_pair<256, false, __nv_bfloat16, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c,
                                                             scale_inv, out, ldo, nullptr, scatter, requant, stream);
     }
+#define BSI_PAIR_F32(BN_) (dbg_iacc ? BSI_PAIR_T(BN_, true, float) : BSI_PAIR_T(BN_, false, float))
     switch (bn) {
         case 256: return BSI_PAIR(256);
+#if BSI_PAIR_LEANFIN
+        case 224: return BSI_PAIR_F32(224);
+        case 192: return BSI_PAIR_F32(192);
+        case 160: return BSI_PAIR_F32(160);
+        case 96: return BSI_PAIR_F32(96);
+#endif
         case 128: return BSI_PAIR(128);
         default: return BSI_PAIR(64);
     }
+#undef BSI_PAIR_F32
 #undef BSI_PAIR
 #undef BSI_PAIR_T
 }

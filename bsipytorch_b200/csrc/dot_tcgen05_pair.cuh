@@ -28,6 +28,16 @@
 // All waits are bounded; a timeout raises the abort flag of both CTAs and every role drains out.
 #pragma once
 
+#ifndef BSI_PAIR_MAGIC
+#define BSI_PAIR_MAGIC 1
+#endif
+#ifndef BSI_PAIR_LEANFIN
+#define BSI_PAIR_LEANFIN 1
+#endif
+#ifndef BSI_PAIR_F32X2
+#define BSI_PAIR_F32X2 0
+#endif
+
 namespace pair {
 
 constexpr int kThreads = 384;
@@ -37,20 +47,28 @@ constexpr int kRegsLow = 40;
 constexpr int kRegsHigh = 232;
 constexpr long long kWait = 500000000ll;  // ~0.25 s; real waits are microseconds
 
+constexpr int kSmemLimit = 232448;   // 227 KB: the most dynamic shared memory one CTA can opt in to
+
 template <int BN>
 struct Cfg {
+    static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "tile width: a multiple of 32 in [64, 256]");
     static constexpr int kHalfN = BN / 2;                 // key rows each CTA loads
     static constexpr int kABytes = BM * BK;               // 16 KB
-    static constexpr int kBBytes = kHalfN * BK;           // 16 / 8 / 4 KB
+    static constexpr int kBBytes = kHalfN * BK;           // 4 .. 16 KB, a multiple of 1 KB (swizzle atom)
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kStoreBytes = kEpiWarps * 4096;  // one 32x32 fp32 block per epilogue warp
-    static constexpr int kStages = (BN == 256) ? 6 : (BN == 128 ? 8 : 9);
     static constexpr int kTmemCols = 512;                 // all of TMEM: 1 CTA per SM anyway
-    static constexpr int kAccBufs = 512 / BN;             // accumulator ring: 2, 4 or 8 buffers of BN columns
-    static constexpr int kBarriers = 2 * kStages + 2 * kAccBufs + 1;
+    // accumulator ring: buffers start at multiples of the next power of two >= BN (2, 4 or 8 buffers)
+    static constexpr int kAccStride = BN > 128 ? 256 : (BN > 64 ? 128 : 64);
+    static constexpr int kAccBufs = 512 / kAccStride;
     // chunk-maximum exchange of the re-quantising epilogue: 2 parities x 8 warps x 32 lanes x 2 bytes + 8 counters
     static constexpr int kXchgBytes = 2 * kEpiWarps * 32 * 2 + kEpiWarps * 4;
+    static constexpr int kFixedBytes = kStoreBytes + (2 * 9 + 2 * kAccBufs + 1) * 8 + 16 + kXchgBytes + 1024;
+    static constexpr int kFit = (kSmemLimit - kFixedBytes) / kStageBytes;
+    static constexpr int kStages = kFit > 9 ? 9 : kFit;   // 6 (BN >= 192), 7, 8, 8, 9 (BN = 64)
+    static constexpr int kBarriers = 2 * kStages + 2 * kAccBufs + 1;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + kBarriers * 8 + 16 + kXchgBytes + 1024;
+    static_assert(kStages >= 4 && kSmemBytes <= kSmemLimit, "operand ring does not fit");
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -150,6 +168,38 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, con
     }
 }
 
+// float(v) for |v| <= 2^22 without a conversion instruction: adding v to the bit pattern of 1.5 * 2^23 gives the
+// float 1.5 * 2^23 + v exactly, and subtracting the constant again is exact too. (A chunk accumulator of 8-bit
+// operands is at most 256 * 128 * 128 = 2^22 in magnitude.) The I2F instruction runs at a sixteenth of the FMA
+// rate per SM; with it the epilogue's 32 K conversions per chunk took longer than the chunk's MMAs.
+__device__ __forceinline__ float int_to_float_exact(int32_t v) {
+#if BSI_PAIR_MAGIC
+    return __int_as_float(v + 0x4B400000) - 12582912.0f;
+#else
+    return static_cast<float>(v);
+#endif
+}
+
+// Two columns at once with the packed float32 instructions of sm_100 (one issue slot for two values):
+// acc = fmaf(float(v), qscale, acc) for both, with the same exact conversion as int_to_float_exact.
+__device__ __forceinline__ void fold_pair(float& a0, float& a1, int32_t v0, int32_t v1, float qscale) {
+    asm("{\n"
+        ".reg .b64 m, q, c, k;\n"
+        ".reg .b32 x0, x1;\n"
+        "add.s32 x0, %2, 0x4B400000;\n"
+        "add.s32 x1, %3, 0x4B400000;\n"
+        "mov.b64 m, {x0, x1};\n"
+        "mov.b64 k, {%5, %5};\n"
+        "add.rn.f32x2 m, m, k;\n"
+        "mov.b64 q, {%4, %4};\n"
+        "mov.b64 c, {%0, %1};\n"
+        "fma.rn.f32x2 c, m, q, c;\n"
+        "mov.b64 {%0, %1}, c;\n"
+        "}"
+        : "+f"(a0), "+f"(a1)
+        : "r"(v0), "r"(v1), "f"(qscale), "f"(-12582912.0f));
+}
+
 // Last step of one output element. float: the raw dot value (the microbenchmark entry point).
 // half / bfloat16: the layer epilogue of the reference, `scores.to(dtype) + bias.to(dtype)`
 // (verify_accuracy_bsi.py:193-195): both terms are narrowed first, added, and narrowed again.
@@ -186,8 +236,8 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const RequantDst requant) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
-    constexpr int kCols = BN / 2;       // accumulator columns per epilogue warp
-    constexpr int kGroups = kCols / 32; // tcgen05.ld / store rounds per warp
+    constexpr int kCols = BN / 2;              // accumulator columns per epilogue warp: a multiple of 16
+    constexpr int kPieces = (kCols + 31) / 32; // tcgen05.ld pieces per warp and chunk
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -245,17 +295,26 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     // Cluster barrier split around the TMEM allocation: arrive now (thread 0's barrier inits are
     // released by its own arrive), wait after the allocation, so the two latencies overlap.
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(C::kTmemCols)) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    const bool is_producer = warp < kFirstEpiWarp && warp != 1;
+    uint32_t tmem_base = 0;
+    if (is_producer) {
+        // The producers need the barriers of both CTAs, not the accumulator memory: they go on to their
+        // first copies while warp 1 is still allocating TMEM.
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(tmem_slot)), "r"(static_cast<uint32_t>(C::kTmemCols)) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        }
+        tc_fence_before();
+        // warp 1 and the eight epilogue warps: the TMEM address is in shared memory from here on
+        asm volatile("bar.sync 1, %0;" ::"n"((1 + kEpiWarps) * 32) : "memory");
+        // both CTAs' barriers are initialised before anyone touches the peer's
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        tc_fence_after();
+        tmem_base = *tmem_slot;
     }
-    tc_fence_before();
-    __syncthreads();
-    // both CTAs' barriers are initialised before anyone touches the peer's
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
 
     // Programmatic dependent launch: everything above (barriers, TMEM, tensor-map prefetch) touched no global
     // memory of an earlier kernel and may run while that kernel drains; from here on its results are needed.
@@ -301,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                     const int b = cc % kAccBufs;
                     const uint32_t tph = static_cast<uint32_t>(cc / kAccBufs) & 1u;
                     if (!wait_or_abort(tempty_bar(b), tph ^ 1u, actx, 3)) { ok = false; break; }
-                    const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(b * BN);
+                    const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(b * C::kAccStride);
 #pragma unroll
                     for (int half = 0; half < 2; ++half, ++it) {
                         const int s = it % kStages;
@@ -376,23 +435,38 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 if (!wait_or_abort(tfull_bar(b), tph, actx, 4)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                                       static_cast<uint32_t>(b * BN + col0);
+                                       static_cast<uint32_t>(b * C::kAccStride + col0);
+                // The warp's kCols columns come in pieces of 32 (the last one 16 when kCols % 32 == 16); the
+                // load of the next piece is in flight while this one is folded into the running sums.
                 int32_t v[2][32];
-                tmem_ld32(taddr, v[0]);
+                if (kCols >= 32) tmem_ld32(taddr, v[0]); else tmem_ld16(taddr, v[0]);
 #pragma unroll
-                for (int j = 0; j < kGroups; ++j) {
+                for (int j = 0; j < kPieces; ++j) {
                     tmem_ld_wait();
-                    if (j + 1 < kGroups) tmem_ld32(taddr + (j + 1) * 32, v[(j + 1) & 1]);
+                    if (j + 1 < kPieces) {
+                        if ((j + 2) * 32 <= kCols) tmem_ld32(taddr + (j + 1) * 32, v[(j + 1) & 1]);
+                        else tmem_ld16(taddr + (j + 1) * 32, v[(j + 1) & 1]);
+                    }
+                    constexpr int kLastWidth = kCols - (kPieces - 1) * 32;
+                    const int width = (j + 1 < kPieces) ? 32 : kLastWidth;
+#if BSI_PAIR_F32X2
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        if (e < width) fold_pair(acc[j * 32 + e], acc[j * 32 + e + 1], v[j & 1][e], v[j & 1][e + 1], qscale);
+                    }
+#else
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
-                        acc[j * 32 + e] = __fmaf_rn(static_cast<float>(v[j & 1][e]), qscale, acc[j * 32 + e]);
+                        if (e < width)
+                            acc[j * 32 + e] = __fmaf_rn(int_to_float_exact(v[j & 1][e]), qscale, acc[j * 32 + e]);
                     }
+#endif
                     if (DBG) {
                         if (row_ok) {
 #pragma unroll
                             for (int e = 0; e < 32; ++e) {
                                 const int col = n0 + col0 + j * 32 + e;
-                                if (col < R)
+                                if (e < width && col < R)
                                     dbg_iacc[(static_cast<int64_t>(row) * R + col) * chunks + c] = v[j & 1][e];
                             }
                         }
@@ -533,6 +607,58 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 row_shift = d * scatter.rows_per_dst;
             }
             if ((store_flags & 1)) {
+                if constexpr (BSI_PAIR_LEANFIN && sizeof(OutT) == 4) {
+                    // float32 output: the raw running sums are transposed first and scaled afterwards, when a
+                    // lane holds four consecutive columns of a row: the key scales (and bias) of those columns
+                    // are four loads per round instead of two shuffles per value (the warp shuffles of the
+                    // other order cost as many cycles as the stores themselves). Rounds of 32 columns, then
+                    // one of 16 when the warp's column count is not a multiple of 32.
+                    float* outf = reinterpret_cast<float*>(outp);
+                    constexpr int kFull = kCols / 32;
+                    constexpr int kRoundsF = kFull + ((kCols % 32) != 0 ? 1 : 0);
+#pragma unroll
+                    for (int g = 0; g < kRoundsF; ++g) {
+                        const bool tail = g == kFull;
+                        const int nch = tail ? 4 : 8;          // 16-byte pieces per staged row
+                        const int cchunk = lane & (nch - 1);
+                        const int col = n0 + col0 + g * 32 + cchunk * 4;
+                        float w[4], bv[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const bool in = col + e < R;
+                            w[e] = in ? __ldg(bw0 + col + e) : 0.0f;
+                            bv[e] = (in && has_bias) ? __ldg(bias + col + e) : 0.0f;
+                        }
+                        uint8_t* dst = my_store + lane * (nch * 16);
+#pragma unroll
+                        for (int ch = 0; ch < 8; ++ch) {
+                            if (ch < nch) {
+                                const int swz = tail ? (ch ^ ((lane >> 1) & 3)) : (ch ^ (lane & 7));
+                                const int j = g * 32 + ch * 4;
+                                *reinterpret_cast<float4*>(dst + (swz << 4)) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                            }
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (i < nch) {
+                                const int rr = i * (32 / nch) + lane / nch;
+                                const int swz = tail ? (cchunk ^ ((rr >> 1) & 3)) : (cchunk ^ (rr & 7));
+                                float4 o = *reinterpret_cast<const float4*>(my_store + rr * (nch * 16) + (swz << 4));
+                                o.x = relu_if<float>(finish<float>((o.x * w[0]) * scale_inv, bv[0], has_bias), relu);
+                                o.y = relu_if<float>(finish<float>((o.y * w[1]) * scale_inv, bv[1], has_bias), relu);
+                                o.z = relu_if<float>(finish<float>((o.z * w[2]) * scale_inv, bv[2], has_bias), relu);
+                                o.w = relu_if<float>(finish<float>((o.w * w[3]) * scale_inv, bv[3], has_bias), relu);
+                                const int grow = row_base + rr;
+                                if (grow < Q && col < R) {   // R is a multiple of 4 on this path
+                                    *reinterpret_cast<float4*>(outf + static_cast<int64_t>(grow - row_shift) * ldo + col) = o;
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                } else {
+                static_assert(kCols % kRoundCols == 0, "this store order needs whole rounds");
 #pragma unroll
                 for (int g = 0; g < kRounds; ++g) {
                     const int colg = n0 + col0 + g * kRoundCols;
@@ -564,6 +690,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                         }
                     }
                     __syncwarp();
+                }
                 }
             } else {
                 OutT* orow = outp + static_cast<int64_t>(row_ok ? row - row_shift : 0) * ldo;
