@@ -63,8 +63,39 @@ def measured_peaks():
     if os.path.exists(p):
         with open(p) as f:
             d = json.load(f)
-        return dict(hbm_gbs=d.get("hbm_gbs"), bf16=d.get("bf16_tflops"), source="measured")
-    return dict(hbm_gbs=6650.0, bf16=1590.0, source="fallback")
+        return dict(hbm_gbs=d.get("hbm_gbs"), bf16=d.get("bf16_tflops"), bf16_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def dot_config(wl):
+    """The `config` object of a dot workload; both arms print the same one."""
+    set_bytes = wl["R"] * wl["D"] + wl["Q"] * wl["D"] + wl["Q"] * wl["R"] * 4
+    nsets = max(2, int(-(-2 * L2_BYTES // set_bytes)))
+    return {"workload": wl["name"],
+            "l2": f"GPU arm: {nsets} rotating operand sets, {nsets * set_bytes / 2**20:.0f} MiB > 126 MiB L2; CPU arm: host memory"}
+
+
+def int8_library_peak(dev):
+    """Dense int8 throughput of the library GEMM on this GPU (torch._int_mm, 8192^3, best of 10, CUDA events):
+    the second denominator beside 2 x the measured bf16 figure."""
+    import torch
+    n = 8192
+    a = torch.randint(-64, 64, (n, n), dtype=torch.int8, device=dev)
+    b = torch.randint(-64, 64, (n, n), dtype=torch.int8, device=dev).t().contiguous().t()
+    for _ in range(3):
+        torch._int_mm(a, b)
+    torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(10):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    del a, b
+    return 2.0 * n ** 3 / (best * 1e-3) / 1e12
 
 
 class ClockSampler:
@@ -189,7 +220,7 @@ def run_reference(args, wl, rank, world):
         "impl": "reference", "metric": "BSI dot effective TOPS", "value": tops, "unit": "TOPS",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-        "config": {"workload": wl["name"], "sample": sample},
+        "config": dot_config(wl),
         "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": "port", "sample": sample},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -366,51 +397,49 @@ OPT_WORKLOADS = {
 }
 
 
-def run_opt(args, rank, world, local_rank):
-    """OPT forward next-token pass with every q/k/v/out/fc1/fc2 linear as a BSI op; tokens/s.
-
-    N > 1: every BSI linear is sharded along its output rows over the ranks and followed by one
-    NCCL all-gather (strong scaling: the batch is fixed)."""
+def measure_opt(workload, steps, warmup, e2e_steps, rank, world, local_rank, opt_impl="tp", exchange="auto", push="store",
+                microbatches=2, cuda_graph=1, kernel_split=False):
+    """Times the OPT forward next-token pass (every q/k/v/out/fc1/fc2 linear a BSI op) inside an initialised
+    process group; returns the measurements as a dict (max over ranks, CUDA events)."""
     import torch
     import torch.distributed as dist
 
     import bsipytorch_b200
     from bsipytorch_b200 import opt
 
-    spec = OPT_WORKLOADS[args.workload]
-    torch.cuda.set_device(local_rank)
+    spec = OPT_WORKLOADS[workload]
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    cfg = opt.CONFIGS[args.workload]
+    cfg = opt.CONFIGS[workload]
     B, T = spec["batch"], spec["seq"]
     dtype = getattr(torch, spec["dtype"])
-    if args.opt_impl == "tp":
+    if opt_impl == "tp":
         # fused QKV key set, head-sharded attention, token-sharded residual stream, packed int8 exchanges
         from bsipytorch_b200.opt_tp import build_opt_tp
-        model = build_opt_tp(args.workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world,
-                             exchange=args.exchange, push=args.push, microbatches=args.microbatches)
-        graphed = bool(args.cuda_graph) and (world == 1 or model.exchange == "peer")
+        model = build_opt_tp(workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world,
+                             exchange=exchange, push=push, microbatches=microbatches)
+        graphed = bool(cuda_graph) and (world == 1 or model.exchange == "peer")
         if graphed:
             model.capture(spec["batch"], spec["seq"])
         # this library's kernels per layer: 4 fused linears + the activation packs (two of them inside the add +
-        # LayerNorm + pack kernel; the fc2 one disappears when fc1 re-quantises in its epilogue) + 6 flag barriers
+        # LayerNorm + pack kernel; the fc2 one disappears when fc1 re-quantises in its epilogue) + the flag barriers
         layer0 = model.layers[0]
-        launches_per_layer = 4 + (3 if layer0.fuse_requant else 4) + (6 if (world > 1 and model.exchange == "peer") else 0)
+        launches_per_layer = 4 + (3 if layer0.fuse_requant else 4) + (getattr(model, "barriers_per_layer", 6) if (world > 1 and model.exchange == "peer") else 0)
         scheme = ("tensor parallel: R-sharded BSI linears, head-sharded attention, token-sharded residual; packed int8 "
                   "activations and linear outputs " + ("stored straight into peer buffers over NVLink by the pack / linear kernels"
                                                        if model.exchange == "peer" else "moved by NCCL all-gather / all-to-all"))
+        exchange_used = model.exchange if world > 1 else "none"
     else:
         # one BSIQuantizedLinear per nn.Linear, each followed by an fp16 all-gather of its outputs
-        model = opt.build_opt_bsi(args.workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world)
+        model = opt.build_opt_bsi(workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world)
         launches_per_layer = 12     # 6 x (pack + fused linear)
         graphed = False
         scheme = "R-sharded BSI linears + fp16 all-gather of every output"
+        exchange_used = "nccl all-gather" if world > 1 else "none"
     ids_host = torch.randint(0, cfg.vocab_size, (B, T), generator=torch.Generator().manual_seed(0)).pin_memory()
     ids = ids_host.to(dev)
     tok_host = torch.empty(B, dtype=torch.long).pin_memory()
-    warmup = max(3, args.warmup)
-    K = args.steps
+    warmup = max(3, warmup)
+    K = steps
 
     def barrier():
         if world > 1:
@@ -430,7 +459,7 @@ def run_opt(args, rank, world, local_rank):
         ev1.record()
         barrier()
         ms = ev0.elapsed_time(ev1)
-        e2e_steps = max(3, min(K, args.e2e_steps))
+        e2e_steps = max(3, min(K, e2e_steps))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
@@ -441,7 +470,7 @@ def run_opt(args, rank, world, local_rank):
         barrier()
         sampler.stop()
         e2e_ms = e0.elapsed_time(e1)
-    if args.kernel_split:
+    if kernel_split:
         # device time per kernel over three more steps (CUPTI records through torch.profiler; informational,
         # printed to stderr by rank 0, outside every timed region)
         import collections
@@ -465,33 +494,56 @@ def run_opt(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = float(t[0]), float(t[1])
     status = bsipytorch_b200.bsi_ops.device_status()
+    st = torch.tensor([status], dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    h, f, L = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers
+    res = dict(B=B, T=T, K=K, warmup=warmup, ms=ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, status=int(st[0]), graphed=graphed,
+               scheme=scheme, exchange=exchange_used, launches=K * L * launches_per_layer, clocks=sampler.summary(),
+               bsi_ops_step=L * 2.0 * B * T * (4 * h * h + 2 * h * f), tok=tok)
+    del model
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_opt(args, rank, world, local_rank):
+    """OPT forward next-token pass with every q/k/v/out/fc1/fc2 linear as a BSI op; tokens/s.
+
+    N > 1: tensor parallel over R-sharded keys (strong scaling: the batch is fixed)."""
+    import torch
+    import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    r = measure_opt(args.workload, args.steps, args.warmup, args.e2e_steps, rank, world, local_rank, args.opt_impl,
+                    args.exchange, args.push, args.microbatches, args.cuda_graph, args.kernel_split)
     if rank == 0:
-        h, f, L = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers
-        bsi_ops_step = L * 2.0 * B * T * (4 * h * h + 2 * h * f)
+        B, T, K, ms = r["B"], r["T"], r["K"], r["ms"]
         peaks = measured_peaks()
         int8_peak = 2.0 * peaks["bf16"]
-        tops = bsi_ops_step * K / (ms * 1e-3) / 1e12 / world
+        tops = r["bsi_ops_step"] * K / (ms * 1e-3) / 1e12 / world
         line = {
             "metric": "OPT BSI tokens/s", "value": B * T * K / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": K, "warmup": warmup, "ms_per_step": ms / K, "higher_is_better": True,
+            "steps": K, "warmup": r["warmup"], "ms_per_step": ms / K, "higher_is_better": True,
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "int8 x int8 -> int32 BSI linears, fp16 elsewhere",
             "data": "synthetic",
             "config": {"workload": f"{args.workload} random init, batch {B} x seq {T} uniform random ids, all q/k/v/out/fc1/fc2 as BSI ops, dp=2, fixed76 chunkscale",
-                       "parallelism": f"{scheme} x{world}" if world > 1 else "1 GPU",
-                       "model_impl": args.opt_impl, "launch": "CUDA graph of the decoder stack" if graphed else "eager",
-                       "push": args.push if (world > 1 and args.opt_impl == "tp") else None,
+                       "parallelism": f"{r['scheme']} x{world}" if world > 1 else "1 GPU",
+                       "model_impl": args.opt_impl, "launch": "CUDA graph of the decoder stack" if r["graphed"] else "eager",
                        "microbatches": args.microbatches if (world > 1 and args.opt_impl == "tp") else 1,
                        "l2": "weights and activations of one forward exceed the 126 MiB L2" if args.workload != "opt-125m" else "keys of one forward (~150 MB with slices) are about the size of L2"},
-            "e2e": {"value": B * T * e2e_steps / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8,
-                    "d2h_bytes_per_step": B * 8, "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps,
+            "e2e": {"value": B * T * r["e2e_steps"] / (r["e2e_ms"] * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * T * 8,
+                    "d2h_bytes_per_step": B * 8, "ms_per_step": r["e2e_ms"] / r["e2e_steps"], "steps": r["e2e_steps"],
                     "path": "pinned host ids -> H2D -> OPTForCausalLM.next_token (BSI linears) -> D2H argmax tokens"},
-            "gpu_launches": K * L * launches_per_layer,
-            "clocks": sampler.summary(),
+            "gpu_launches": r["launches"],
+            "clocks": r["clocks"],
             "roofline": {"bound": "tensor", "achieved": tops, "peak": int8_peak, "unit": "TFLOP/s", "frac": tops / int8_peak,
                          "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16']}", "traffic": None,
-                         "kernel": "dot_i8_tcgen05 (whole-step time: includes pack, attention, LayerNorm, all-gather)",
-                         "algorithmic_ops_per_step": bsi_ops_step},
-            "device_status": status,
+                         "kernel": "dot_i8_tcgen05 (whole-step time: includes pack, attention, LayerNorm, exchange)",
+                         "algorithmic_ops_per_step": r["bsi_ops_step"]},
+            "device_status": r["status"],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -518,6 +570,12 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=30)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--engine", default="tcgen05")
+    ap.add_argument("--repeats", type=int, default=50, help="dot workloads: how many times the K-step region is timed")
+    ap.add_argument("--sustained-seconds", type=float, default=1.5, help="dot workloads: length of the sustained leg (0 = skip)")
+    ap.add_argument("--isolated", type=int, default=30, help="dot workloads: single launches timed after an L2 flush (0 = skip)")
+    ap.add_argument("--extras", type=int, default=1,
+                    help="fc1: also report the FC2 dot (1 GPU), OPT-6.7B tokens/s on the same ranks and the library int8 GEMM rate")
+    ap.add_argument("--opt-steps", type=int, default=8, help="fc1 extras: timed OPT-6.7B forwards")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -633,20 +691,64 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The timed region is exactly K steps between two barriers; it is taken `repeats` times (default 50) so that the
+    # reported value is the median region, with the best and the spread beside it.
     K = args.steps
     reps, rem = divmod(K, nsets)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    region_ms = []
     sampler.start()
-    ev0.record()
-    for _ in range(reps):
-        graph.replay()
-    for i in range(rem):
-        step(i)
-    ev1.record()
-    barrier()
-    ms = ev0.elapsed_time(ev1)
+    for _ in range(max(1, args.repeats)):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(reps):
+            graph.replay()
+        for i in range(rem):
+            step(i)
+        ev1.record()
+        barrier()
+        region_ms.append(ev0.elapsed_time(ev1))
+    sampler.stop()
+    clocks = sampler.summary()
     launches = K
+
+    # Sustained leg: back-to-back replays for at least args.sustained_seconds, its own clock record (the power cap
+    # pulls the SM clock down within a second of dense tensor work).
+    sustained = None
+    if args.sustained_seconds > 0:
+        s2 = ClockSampler(local_rank)
+        n_rep = max(1, int(args.sustained_seconds / max(1e-6, (sorted(region_ms)[len(region_ms) // 2] * 1e-3) * nsets / K)) // 8)
+        es0, es1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        s2.start()
+        t_wall = time.perf_counter()
+        es0.record()
+        total_steps = 0
+        while True:
+            for _ in range(n_rep):
+                graph.replay()
+            total_steps += n_rep * nsets
+            torch.cuda.synchronize()
+            if time.perf_counter() - t_wall >= args.sustained_seconds:
+                break
+        es1.record()
+        barrier()
+        s2.stop()
+        sustained = (es0.elapsed_time(es1), total_steps, s2.summary())
+
+    # Isolated launches: one dot after an L2 flush (a 256 MiB fill), CUDA events around the single launch.
+    isolated_us = []
+    if args.isolated > 0:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        for i in range(args.isolated):
+            flush.fill_(i & 1)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            step(i)
+            a1.record()
+            torch.cuda.synchronize()
+            isolated_us.append(a0.elapsed_time(a1) * 1e3)
+        del flush
 
     # End to end through the public entry points, host buffers in and out. Two streams alternate, each with its own
     # pinned output buffer, so that the 16.8 MB device-to-host read of one step overlaps the upload, pack and dot of
@@ -681,47 +783,92 @@ def main():
         cur.wait_stream(ln)
     e1.record()
     barrier()
-    sampler.stop()
     out_host = out_hosts[(args.e2e_steps - 1) % 2]
     e2e_ms = e0.elapsed_time(e1)
     assert torch.equal(out_host, want_out.cpu())
 
-    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor(region_ms + [e2e_ms, sustained[0] if sustained else 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = float(t[0]), float(t[1])
+    region_ms = sorted(float(v) for v in t[:len(region_ms)])
+    e2e_ms, sus_ms = float(t[-2]), float(t[-1])
+    ms = region_ms[len(region_ms) // 2]
     status = ops.device_status()
+
+    # The second dot shape of the metric (N = 1 only): same protocol, fewer repeats.
+    fc2_block = None
+    if world == 1 and args.workload == "fc1" and args.extras:
+        fc2_block = time_fc2(dev, ops, L, capi)
+    for s_ in sets:
+        s_.clear()
+    del sets
+    torch.cuda.empty_cache()
+
+    # The other half of the metric: OPT-6.7B tokens/s on the same ranks (tensor parallel, strong scaling).
+    opt_block = None
+    if args.extras and args.workload == "fc1":
+        try:
+            r = measure_opt("opt-6.7b", args.opt_steps, 3, 3, rank, world, local_rank, "tp", args.exchange, args.push,
+                            args.microbatches, args.cuda_graph)
+            opt_block = {"tokens_per_s": r["B"] * r["T"] * r["K"] / (r["ms"] * 1e-3), "ms_per_step": r["ms"] / r["K"],
+                         "steps": r["K"], "warmup": r["warmup"], "batch": r["B"], "seq": r["T"], "exchange": r["exchange"],
+                         "status": r["status"], "scaling": "strong", "launch": "CUDA graph of the decoder stack" if r["graphed"] else "eager",
+                         "e2e_tokens_per_s": r["B"] * r["T"] * r["e2e_steps"] / (r["e2e_ms"] * 1e-3), "clocks": r["clocks"],
+                         "bsi_tops_per_gpu": r["bsi_ops_step"] * r["K"] / (r["ms"] * 1e-3) / 1e12 / world}
+        except Exception as e:      # the headline line must not be lost to the secondary block
+            opt_block = {"unavailable": str(e)[:300]}
 
     if rank == 0:
         ops_step = 2.0 * Q * R * D * world
         tops = ops_step * K / (ms * 1e-3) / 1e12
+        best_tops = ops_step * K / (region_ms[0] * 1e-3) / 1e12
         e2e_tops = ops_step * args.e2e_steps / (e2e_ms * 1e-3) / 1e12
         peaks = measured_peaks()
         int8_peak = 2.0 * peaks["bf16"]
         per_gpu_tops = tops / world
         alg_bytes = Q * 7 * D // 8 + R * 6 * D // 8 + Q * chunks * 4 + R * 4 + Q * R * 4
+        lib_peak = int8_library_peak(dev) if args.extras else None
+        mhz = clocks.get("sm_mhz")
         line = {
             "metric": "BSI dot effective TOPS", "value": tops, "unit": "TOPS", "n_gpus": world, "steps": K,
             "warmup": warmup, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 x int8 -> int32 (bit-exact with the sliced popcount), fp32 chunk combine",
             "data": "synthetic",
-            "config": {"workload": wl["name"], "engine": args.engine, "keys_per_gpu": R,
-                       "l2": f"{nsets} rotating operand sets, {nsets * set_bytes / 2**20:.0f} MiB > 126 MiB L2",
-                       "launch": f"CUDA graph of {nsets} steps replayed"},
+            "config": dot_config(wl),
+            "run": {"engine": args.engine, "keys_per_gpu": R, "launch": f"CUDA graph of {nsets} steps replayed",
+                    "timed_region": f"{K} steps between barriers, taken {len(region_ms)} times: value = median region, max over ranks per region"},
+            "timing": {"regions": len(region_ms), "median_us_per_step": 1e3 * ms / K, "best_us_per_step": 1e3 * region_ms[0] / K,
+                       "worst_us_per_step": 1e3 * region_ms[-1] / K, "best_tops": best_tops,
+                       "sm_cycles_per_step": (1e3 * ms / K) * mhz if mhz else None,
+                       "isolated_launch_us": ({"median": sorted(isolated_us)[len(isolated_us) // 2], "min": min(isolated_us), "launches": len(isolated_us),
+                                               "how": "one dot after a 256 MiB L2 flush, CUDA events around the single launch (includes launch latency)"}
+                                              if isolated_us else None)},
             "e2e": {"value": e2e_tops, "unit": "TOPS", "h2d_bytes_per_step": Q * D * 2,
                     "d2h_bytes_per_step": Q * R * 4, "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps,
                     "path": "pinned host fp16 -> H2D -> build_bsi_queries_cuda_batch_packed -> batch_dot_product_multiquery_cuda_batch_caps -> D2H fp32 (two streams alternate, so one step's download overlaps the next step's upload and compute)"},
             "gpu_launches": launches,
-            "clocks": sampler.summary(),
+            "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": per_gpu_tops, "peak": int8_peak, "unit": "TFLOP/s",
                          "frac": per_gpu_tops / int8_peak,
                          "peak_source": f"2 x {peaks['source']} bf16 burst {peaks['bf16']} (dense int8 = 2 x bf16 on this part)",
                          "traffic": NCU_TRAFFIC_BYTES[args.workload] if args.engine == "tcgen05" else None,
                          "kernel": {"tcgen05": "dot_i8_tcgen05_pair_kernel", "bmma": "dot_words_bmma_kernel", "simt": "dot_i8_simt_kernel"}.get(args.engine, "dot_i8_tcgen05_pair_kernel"),
                          "algorithmic_ops_per_launch": 2.0 * Q * R * D, "algorithmic_bytes_per_launch": alg_bytes,
-                         "hbm_frac_of_measured": (alg_bytes / (ms / K * 1e-3) / 1e9) / peaks["hbm_gbs"]},
+                         "hbm_frac_of_measured": (alg_bytes / (ms / K * 1e-3) / 1e9) / peaks["hbm_gbs"],
+                         "library_int8_gemm_tops": lib_peak,
+                         "frac_of_library_int8_gemm": (per_gpu_tops / lib_peak) if lib_peak else None},
             "device_status": status,
         }
+        if sustained is not None:
+            sus_tops = ops_step * sustained[1] / (sus_ms * 1e-3) / 1e12
+            sus_peak = 2.0 * peaks["bf16_sustained"] if peaks.get("bf16_sustained") else None
+            line["sustained"] = {"seconds": sus_ms * 1e-3, "steps": sustained[1], "value": sus_tops, "unit": "TOPS",
+                                 "peak": sus_peak, "frac": (sus_tops / world / sus_peak) if sus_peak else None,
+                                 "peak_source": "2 x measured bf16 sustained", "clocks": sustained[2]}
+        if fc2_block is not None:
+            line["fc2"] = fc2_block
+        if opt_block is not None:
+            line["opt_6_7b"] = opt_block
         if world == 1:
             cpu_tops, sample, secs, cores = cpu_port_rate(q, k, args.cpu_seconds)
             line["cpu_baseline"] = {"value": cpu_tops, "unit": "TOPS", "cores": cores, "kind": "port",
@@ -729,6 +876,68 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def time_fc2(dev, ops, L, capi):
+    """FC2-like dot (Q=512, R=2048, D=8192) with the protocol of the headline: rotating operand sets, graph replays,
+    median of 20 regions of 400 steps."""
+    import ctypes as C
+
+    import torch
+    wl = WORKLOADS["fc2"]
+    Q, R, D = wl["Q"], wl["R"], wl["D"]
+    chunks = D // 256
+    q, k = make_inputs(wl, seed=123)
+    keys_cap, *_ = ops.build_bsi_keys_cuda(k.to(dev), 2, 0.5)
+    kt = ops.debug_keys_tensors(keys_cap)
+    qcap = ops.build_bsi_queries_cuda_batch_packed(q.to(dev), 2, 0.5)
+    qt = ops.debug_query_batch_tensors(qcap)
+    set_bytes = kt["q8"].numel() + qt["q8"].numel() + Q * R * 4
+    nsets = max(2, int(-(-2 * L2_BYTES // set_bytes)))
+    sets = [dict(a8=qt["q8"].clone(), qs=qt["scales"].clone(), k8=kt["q8"].clone(), bw0=kt["scales"].clone(),
+                 out=torch.empty(Q, R, dtype=torch.float32, device=dev)) for _ in range(nsets)]
+    scale_inv = C.c_float(float(1.0 / 10.0 ** 4))
+
+    def step(i):
+        s = sets[i % nsets]
+        capi.check(L.bsi_b200_dot_i8(capi.ptr(s["a8"]), s["a8"].shape[1], capi.ptr(s["qs"]), chunks, capi.ptr(s["k8"]),
+                                     s["k8"].shape[1], capi.ptr(s["bw0"]), Q, R, chunks, scale_inv, capi.ptr(s["out"]),
+                                     R, None, capi.ENGINE_TCGEN05, capi.stream_ptr()), "bsi_b200_dot_i8")
+    for i in range(nsets):
+        step(i)
+    torch.cuda.synchronize()
+    want, *_ = ops.batch_dot_product_multiquery_cuda_batch_caps(qcap, keys_cap)
+    assert torch.equal(sets[0]["out"], want)
+    side = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        step(0)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(nsets):
+                step(i)
+    torch.cuda.synchronize()
+    graph.replay()
+    K = 400
+    reps = max(1, K // nsets)
+    K = reps * nsets
+    regions = []
+    for _ in range(20):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        regions.append(e0.elapsed_time(e1))
+    regions.sort()
+    ms = regions[len(regions) // 2]
+    tops = 2.0 * Q * R * D * K / (ms * 1e-3) / 1e12
+    peaks = measured_peaks()
+    return {"workload": wl["name"], "value": tops, "unit": "TOPS", "us_per_step": 1e3 * ms / K, "best_us_per_step": 1e3 * regions[0] / K,
+            "steps": K, "regions": len(regions), "frac": tops / (2.0 * peaks["bf16"]),
+            "l2": f"{nsets} rotating operand sets, {nsets * set_bytes / 2**20:.0f} MiB"}
 
 
 if __name__ == "__main__":

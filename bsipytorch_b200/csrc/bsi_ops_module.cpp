@@ -53,7 +53,14 @@ void check_clip() {
 }
 int engine_from_env() {
     const char* s = std::getenv("BSI_B200_ENGINE");
-    if (!s || !*s || std::string(s) == "auto") return BSI_ENGINE_AUTO;
+    if (!s || !*s || std::string(s) == "auto") {
+        // BSI_TC_DOT=0 is the reference's switch to its non-tensor-core kernel, re-read on every launch
+        // (bsi_cuda_kernels_dot.cuh:2642); here it selects the CUDA-core (dp4a) engine, which evaluates the
+        // same recurrence, so verify_tc_dot_correctness.py compares two engines as it does in the reference.
+        const char* tc = std::getenv("BSI_TC_DOT");
+        if (tc && *tc && std::atoi(tc) == 0) return BSI_ENGINE_SIMT;
+        return BSI_ENGINE_AUTO;
+    }
     const std::string v(s);
     if (v == "tcgen05") return BSI_ENGINE_TCGEN05;
     if (v == "simt") return BSI_ENGINE_SIMT;

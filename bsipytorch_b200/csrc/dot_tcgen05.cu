@@ -485,11 +485,11 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
-// Pair kernel tile width. A CTA spends about (128 + BN / 2) * 256 bytes of operand delivery per chunk, at roughly
-// 50 bytes per clock from L2 into shared memory, which for every width outweighs the 4 * BN tensor-pipe clocks of
-// the chunk; a pair's time is that per chunk times the tiles it walks through. The widest tile wins unless a
-// narrower one needs fewer rounds over the pairs. float32 output may use any multiple of 32, the 16-bit layer
-// epilogues (whole 64-column store rounds) the powers of two.
+// Pair kernel tile width. Measured on the 512 x 8192 x 2048 shape, a pair spends about 650 + 3.1 * BN cycles per
+// 256-deep chunk of a tile (the epilogue's per-column work plus a fixed hand-off cost), and walks through
+// ceil(tiles / pairs) tiles. The widest tile wins unless a narrower one is clearly cheaper (more than 8 %: at equal
+// rounds the wider tile also has the shorter fill and store phases). float32 output may use any multiple of 32,
+// the 16-bit layer epilogues (whole 64-column store rounds) the powers of two.
 int pick_bn_pair(int64_t Q, int64_t R, bool any_width) {
     const int pairs = sm_count() / 2;
     const int64_t mt = (Q + 255) / 256;
@@ -499,8 +499,8 @@ int pick_bn_pair(int64_t Q, int64_t R, bool any_width) {
         if (!any_width && bn != 256 && bn != 128 && bn != 64) continue;
         const int64_t tiles = mt * ((R + bn - 1) / bn);
         const int64_t waves = (tiles + pairs - 1) / pairs;
-        const double cost = static_cast<double>(waves) * (655.0 + 2.56 * bn);
-        if (cost < best_cost * 0.999) {
+        const double cost = static_cast<double>(waves) * (650.0 + 3.1 * bn);
+        if (cost < best_cost * 0.92) {
             best_cost = cost;
             best = bn;
         }
@@ -588,12 +588,10 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
 #define BSI_PAIR_F32(BN_) (dbg_iacc ? BSI_PAIR_T(BN_, true, float) : BSI_PAIR_T(BN_, false, float))
     switch (bn) {
         case 256: return BSI_PAIR(256);
-#if BSI_PAIR_LEANFIN
         case 224: return BSI_PAIR_F32(224);
         case 192: return BSI_PAIR_F32(192);
         case 160: return BSI_PAIR_F32(160);
         case 96: return BSI_PAIR_F32(96);
-#endif
         case 128: return BSI_PAIR(128);
         default: return BSI_PAIR(64);
     }

@@ -11,6 +11,9 @@
 // the TMA producer runs ahead into the next tile while the epilogue of the current one drains, and
 // the fp32 result leaves through shared memory as coalesced stores that overlap the next tile's MMAs.
 //
+// Tile = 256 query rows x BN key rows, BN any multiple of 32 up to 256 (float32 output; the 16-bit layer
+// epilogues use 64, 128 or 256): tcgen05.mma with M = 256 takes every N that is a multiple of 16.
+//
 // Roles per CTA (12 warps; register budget moved with setmaxnreg):
 //   warps 0, 2, 3 TMA producers, k-blocks round robin (both CTAs; every load signals the LEADER's
 //                 full barrier)
@@ -23,20 +26,14 @@
 //   empty[s]   local in each CTA: tcgen05.commit (multicast to both CTAs) after the stage's MMAs
 //   tfull[b]   local in each CTA: multicast commit after a chunk's 8 MMAs
 //   tempty[b]  leader's copy used: one arrival per epilogue warp of BOTH CTAs (16)
-// The accumulator ring holds 512 / BN buffers (2, 4 or 8): with narrow tiles the MMA issuer runs
+// The accumulator ring holds 2, 4 or 8 buffers (BN > 128, > 64, = 64): with narrow tiles the MMA issuer runs
 // several chunks ahead of the epilogue, which takes the barrier round trip off the critical path.
+// What bounds a chunk on wide tiles is the epilogue, not the 8 MMAs (1024 cycles at BN = 256): three
+// instructions per accumulator value (integer add, float add, FMA; see int_to_float_exact) at one warp
+// instruction per clock and SM sub-partition, next to TMEM loads that slow down while the tensor pipe
+// reads and writes its accumulators; measured about 1450 cycles per chunk at BN = 256.
 // All waits are bounded; a timeout raises the abort flag of both CTAs and every role drains out.
 #pragma once
-
-#ifndef BSI_PAIR_MAGIC
-#define BSI_PAIR_MAGIC 1
-#endif
-#ifndef BSI_PAIR_LEANFIN
-#define BSI_PAIR_LEANFIN 1
-#endif
-#ifndef BSI_PAIR_F32X2
-#define BSI_PAIR_F32X2 0
-#endif
 
 namespace pair {
 
@@ -170,34 +167,10 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, con
 
 // float(v) for |v| <= 2^22 without a conversion instruction: adding v to the bit pattern of 1.5 * 2^23 gives the
 // float 1.5 * 2^23 + v exactly, and subtracting the constant again is exact too. (A chunk accumulator of 8-bit
-// operands is at most 256 * 128 * 128 = 2^22 in magnitude.) The I2F instruction runs at a sixteenth of the FMA
-// rate per SM; with it the epilogue's 32 K conversions per chunk took longer than the chunk's MMAs.
+// operands is at most 256 * 128 * 128 = 2^22 in magnitude.) An integer add and a float add on the full-rate
+// pipes instead of one conversion on the slow one.
 __device__ __forceinline__ float int_to_float_exact(int32_t v) {
-#if BSI_PAIR_MAGIC
     return __int_as_float(v + 0x4B400000) - 12582912.0f;
-#else
-    return static_cast<float>(v);
-#endif
-}
-
-// Two columns at once with the packed float32 instructions of sm_100 (one issue slot for two values):
-// acc = fmaf(float(v), qscale, acc) for both, with the same exact conversion as int_to_float_exact.
-__device__ __forceinline__ void fold_pair(float& a0, float& a1, int32_t v0, int32_t v1, float qscale) {
-    asm("{\n"
-        ".reg .b64 m, q, c, k;\n"
-        ".reg .b32 x0, x1;\n"
-        "add.s32 x0, %2, 0x4B400000;\n"
-        "add.s32 x1, %3, 0x4B400000;\n"
-        "mov.b64 m, {x0, x1};\n"
-        "mov.b64 k, {%5, %5};\n"
-        "add.rn.f32x2 m, m, k;\n"
-        "mov.b64 q, {%4, %4};\n"
-        "mov.b64 c, {%0, %1};\n"
-        "fma.rn.f32x2 c, m, q, c;\n"
-        "mov.b64 {%0, %1}, c;\n"
-        "}"
-        : "+f"(a0), "+f"(a1)
-        : "r"(v0), "r"(v1), "f"(qscale), "f"(-12582912.0f));
 }
 
 // Last step of one output element. float: the raw dot value (the microbenchmark entry point).
@@ -237,7 +210,6 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     constexpr int kCols = BN / 2;              // accumulator columns per epilogue warp: a multiple of 16
-    constexpr int kPieces = (kCols + 31) / 32; // tcgen05.ld pieces per warp and chunk
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -275,20 +247,19 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     actx.flag = abort_flag;
     actx.peer_flag = map_to_cta(smem_u32(const_cast<int*>(abort_flag)), rank ^ 1u);
 
-    if (threadIdx.x == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+    if (warp == 0) {
+        // one barrier per lane: full[s], empty[s], tfull[b] and drain count 1 arrival, tempty[b] one per epilogue
+        // warp of both CTAs
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+            *abort_flag = 0;
         }
-        for (int b = 0; b < kAccBufs; ++b) {
-            mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 2 * kEpiWarps);
+        if (lane < kEpiWarps) xchg_count[lane] = 0u;
+        for (int i = lane; i < C::kBarriers; i += 32) {
+            const bool is_tempty = i >= 2 * kStages + kAccBufs && i < 2 * kStages + 2 * kAccBufs;
+            mbar_init(bar_base + 8u * i, is_tempty ? 2 * kEpiWarps : 1);
         }
-        mbar_init(drain_bar, 1);
-        *abort_flag = 0;
-        for (int w = 0; w < kEpiWarps; ++w) xchg_count[w] = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
@@ -436,45 +407,48 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                        static_cast<uint32_t>(b * C::kAccStride + col0);
-                // The warp's kCols columns come in pieces of 32 (the last one 16 when kCols % 32 == 16); the
-                // load of the next piece is in flight while this one is folded into the running sums.
+                // The warp's kCols columns come in pieces of up to 64 (two loads issued back to back, one wait):
+                // under the tensor pipe's own accumulator traffic a TMEM load takes a few hundred cycles, and the
+                // fewer round trips a chunk needs, the sooner its buffer goes back to the MMA issuer. While this
+                // warp waits, the other epilogue warp of the SM sub-partition folds its piece.
                 int32_t v[2][32];
-                if (kCols >= 32) tmem_ld32(taddr, v[0]); else tmem_ld16(taddr, v[0]);
+                constexpr int kSuper = (kCols + 63) / 64;
 #pragma unroll
-                for (int j = 0; j < kPieces; ++j) {
+                for (int sp = 0; sp < kSuper; ++sp) {
+                    const int c0 = sp * 64;
+                    const int wsp = (kCols - c0) < 64 ? (kCols - c0) : 64;   // 64, 48, 32 or 16
+                    if (wsp >= 32) tmem_ld32(taddr + c0, v[0]); else tmem_ld16(taddr + c0, v[0]);
+                    if (wsp == 64) tmem_ld32(taddr + c0 + 32, v[1]);
+                    else if (wsp == 48) tmem_ld16(taddr + c0 + 32, v[1]);
                     tmem_ld_wait();
-                    if (j + 1 < kPieces) {
-                        if ((j + 2) * 32 <= kCols) tmem_ld32(taddr + (j + 1) * 32, v[(j + 1) & 1]);
-                        else tmem_ld16(taddr + (j + 1) * 32, v[(j + 1) & 1]);
+                    if (sp + 1 == kSuper) {
+                        // every column of the buffer is in registers: hand it back before the last piece is folded in
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8u * b);
                     }
-                    constexpr int kLastWidth = kCols - (kPieces - 1) * 32;
-                    const int width = (j + 1 < kPieces) ? 32 : kLastWidth;
-#if BSI_PAIR_F32X2
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        if (e < width) fold_pair(acc[j * 32 + e], acc[j * 32 + e + 1], v[j & 1][e], v[j & 1][e + 1], qscale);
-                    }
-#else
+                    for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        if (e < width)
-                            acc[j * 32 + e] = __fmaf_rn(int_to_float_exact(v[j & 1][e]), qscale, acc[j * 32 + e]);
+                        for (int e = 0; e < 32; ++e) {
+                            if (h * 32 + e < wsp)
+                                acc[c0 + h * 32 + e] = __fmaf_rn(int_to_float_exact(v[h][e]), qscale, acc[c0 + h * 32 + e]);
+                        }
                     }
-#endif
                     if (DBG) {
                         if (row_ok) {
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) {
-                                const int col = n0 + col0 + j * 32 + e;
-                                if (e < width && col < R)
-                                    dbg_iacc[(static_cast<int64_t>(row) * R + col) * chunks + c] = v[j & 1][e];
+                            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                                for (int e = 0; e < 32; ++e) {
+                                    const int col = n0 + col0 + c0 + h * 32 + e;
+                                    if (h * 32 + e < wsp && col < R)
+                                        dbg_iacc[(static_cast<int64_t>(row) * R + col) * chunks + c] = v[h][e];
+                                }
                             }
                         }
                     }
                 }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8u * b);
             }
             if (!ok) break;
 
@@ -607,7 +581,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 row_shift = d * scatter.rows_per_dst;
             }
             if ((store_flags & 1)) {
-                if constexpr (BSI_PAIR_LEANFIN && sizeof(OutT) == 4) {
+                if constexpr (sizeof(OutT) == 4) {
                     // float32 output: the raw running sums are transposed first and scaled afterwards, when a
                     // lane holds four consecutive columns of a row: the key scales (and bias) of those columns
                     // are four loads per round instead of two shuffles per value (the warp shuffles of the

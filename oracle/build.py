@@ -10,7 +10,14 @@ Two artefacts, both git-ignored:
 * ``oracle/_ref/ref_kernels.so`` -- the reference's own CUDA kernels
   (``bsi_ops/csrc/cuda/bsi_cuda_kernels.cu`` and the five ``.cuh`` files it includes),
   compiled for sm_100a straight from the reference checkout. Only built where that
-  checkout exists; no reference source is copied.
+  checkout exists.
+* ``oracle/_ref/benchmarks/*.py`` -- the reference's caller scripts (layer replacement,
+  dot microbenchmark, tensor-core check, apples-to-apples benchmark), staged unmodified so
+  that the GPU tests can run them over this library on a machine without the checkout.
+  Git-ignored like the rest of ``_ref``: they never enter the history.
+
+The reference checkout is looked for in ``$BSI_REFERENCE_DIR`` or, when that is unset, in a
+directory named ``reference`` beside this repository; when neither exists both steps are skipped.
 """
 from __future__ import annotations
 
@@ -24,8 +31,11 @@ BUILD_DIR = os.path.join(HERE, "_build")
 REF_DIR = os.path.join(HERE, "_ref")
 ORACLE_SO = os.path.join(BUILD_DIR, "libbsi_oracle.so")
 REF_SO = os.path.join(REF_DIR, "ref_kernels.so")
-REFERENCE_CHECKOUT = os.environ.get("BSI_REFERENCE_DIR", "/root/reference")
+REFERENCE_CHECKOUT = os.environ.get("BSI_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_KERNEL_TU = os.path.join(REFERENCE_CHECKOUT, "bsi_ops", "csrc", "cuda", "bsi_cuda_kernels.cu")
+REF_CALLERS_DIR = os.path.join(REF_DIR, "benchmarks")
+REF_CALLERS = ["verify_accuracy_bsi.py", "benchmark_dot_kernel_micro.py", "verify_tc_dot_correctness.py",
+               "benchmark_apples_to_apples_bsi.py"]
 
 
 def _host_tag() -> str:
@@ -95,6 +105,21 @@ def build_ref(force: bool = False):
     return REF_SO
 
 
+def stage_reference_callers():
+    """Copy the reference's caller scripts, byte for byte, into ``oracle/_ref/benchmarks`` (where the
+    checkout is present). Returns the directory, or None when there is nothing staged."""
+    import shutil
+    src_dir = os.path.join(REFERENCE_CHECKOUT, "bsi_ops", "benchmarks")
+    if os.path.isdir(src_dir):
+        os.makedirs(REF_CALLERS_DIR, exist_ok=True)
+        for name in REF_CALLERS:
+            src = os.path.join(src_dir, name)
+            if os.path.exists(src):
+                shutil.copyfile(src, os.path.join(REF_CALLERS_DIR, name))
+    return REF_CALLERS_DIR if os.path.isdir(REF_CALLERS_DIR) else None
+
+
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    print(stage_reference_callers())

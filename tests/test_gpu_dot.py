@@ -16,8 +16,8 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 # 1000 + n pins single-CTA tiles of width n; 3000 + n pins paired-CTA (cta_group::2) tiles of width n
 ENGINES = {"simt": capi.ENGINE_SIMT, "tcgen05": capi.ENGINE_TCGEN05, "tcgen05_bn64": 1064,
-           "tcgen05_bn128": 1128, "tcgen05_bn256": 1256, "pair_bn64": 3064, "pair_bn128": 3128,
-           "pair_bn256": 3256}
+           "tcgen05_bn128": 1128, "tcgen05_bn256": 1256, "pair_bn64": 3064, "pair_bn96": 3096, "pair_bn128": 3128,
+           "pair_bn160": 3160, "pair_bn192": 3192, "pair_bn224": 3224, "pair_bn256": 3256}
 
 
 def _prepare(q, k, bits_q=7, bits_k=6, chunk_mode=True, dp=2):
@@ -129,6 +129,24 @@ def test_dot_matches_reference_kernels():
             out = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), ENGINES[engine])
             assert torch.equal(out, ref), engine
         assert torch.equal(H.dot_words(qa["words"], qa["scales"], kb["words"], Bw, o.scale_inv(2)), ref)
+
+
+def test_pair_kernel_fc1_matches_reference_kernels():
+    """The kernel the benchmark times (paired CTAs, automatic tile width at Q = 512) against the reference's own
+    fixed76 kernels on the full FC1 operands, and every other tile width on a 512 x 1024 column block."""
+    from oracle import ref_gpu
+    if not ref_gpu.available():
+        pytest.skip("reference kernels not built on this machine")
+    q, k = _inputs.fc1()
+    qa, kb, Bw = _prepare(q, k)
+    si = o.scale_inv(2)
+    ref = ref_gpu.dot_fixed76(qa["words"], qa["scales"], kb["words"], Bw, si)
+    out = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], si, capi.ENGINE_TCGEN05)
+    assert torch.equal(out, ref)
+    for width in (64, 96, 128, 160, 192, 224, 256):
+        out = H.dot_i8(qa["q8"], qa["scales"], kb["q8"][:1024].contiguous(), kb["scales"][:1024].contiguous(), si, 3000 + width)
+        assert torch.equal(out, ref[:, :1024]), width
+    assert capi.device_status() == 0
 
 
 @pytest.mark.parametrize("cfg", ["fc1", "fc2"])

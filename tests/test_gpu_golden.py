@@ -27,7 +27,8 @@ def test_pack_and_dot_against_reference_outputs(g, name):
     np.testing.assert_array_equal(H.as_u64(kb["words"]), g[f"{name}_k_words"])
     np.testing.assert_array_equal(kb["scales"].cpu().numpy(), g[f"{name}_k_scales"])
     want = g[f"{name}_out"].view(np.uint32)
-    for engine in (capi.ENGINE_TCGEN05, capi.ENGINE_SIMT, 1064, 1128):
+    # 1xxx: single-CTA tiles of that width; 3xxx: the paired-CTA kernel (the one the benchmark times), every width
+    for engine in (capi.ENGINE_TCGEN05, capi.ENGINE_SIMT, 1064, 1128, 3064, 3096, 3128, 3160, 3192, 3224, 3256):
         out = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), engine)
         np.testing.assert_array_equal(out.cpu().numpy().view(np.uint32), want)
     Bw = torch.from_numpy(g[f"{name}_Bw"]).to(DEV)

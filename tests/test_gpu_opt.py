@@ -83,15 +83,18 @@ def test_tensor_parallel_forward_on_one_rank_equals_the_per_linear_model():
         with torch.no_grad():
             want, got = ref(ids), tp(ids)
         assert torch.isfinite(got).all()
-        if dtype == torch.float32:
-            assert torch.equal(got, want)        # every fused piece is exact; LayerNorm stays torch's in float32
-            assert torch.equal(tp.next_token(ids), ref.next_token(ids))
-        else:
-            # 16-bit layer types run the library's own add + LayerNorm + pack kernel: same formula as torch's
-            # LayerNorm, float32 statistics in another summation order, so the last bit of an activation may differ
-            rel = float((got.float() - want.float()).norm() / want.float().norm())
-            assert rel < 2e-2, rel
-            assert (tp.next_token(ids) == ref.next_token(ids)).float().mean() >= 0.75
+        # every fused piece (QKV key set, ReLU and re-quantisation inside the fc1 epilogue) is exact and LayerNorm is
+        # torch's: the logits are those of the per-linear model bit for bit, in every layer type
+        assert torch.equal(got, want)
+        assert torch.equal(tp.next_token(ids), ref.next_token(ids))
+        if dtype == torch.float16:
+            # opt-in add + LayerNorm + pack kernel: same formula as torch's LayerNorm, float32 statistics in another
+            # summation order; the rare last-bit difference is amplified by the following re-quantisations
+            fused = build_opt_tp(cfg, dtype=dtype, device=DEV, seed=11, fuse_ln=True)
+            with torch.no_grad():
+                gf = fused(ids)
+            rel = float((gf.float() - want.float()).norm() / want.float().norm())
+            assert torch.isfinite(gf).all() and rel < 5e-2, rel
         tp.capture(4, 32)                                   # replayed from a CUDA graph: same values
         assert torch.equal(tp(ids), got)
         ids2 = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(9)).to(DEV)
