@@ -397,8 +397,8 @@ OPT_WORKLOADS = {
 }
 
 
-def measure_opt(workload, steps, warmup, e2e_steps, rank, world, local_rank, opt_impl="tp", exchange="auto", push="store",
-                microbatches=2, cuda_graph=1, kernel_split=False):
+def measure_opt(workload, steps, warmup, e2e_steps, rank, world, local_rank, opt_impl="tp", exchange="auto",
+                microbatches=2, cuda_graph=1, kernel_split=False, fuse_ln=False):
     """Times the OPT forward next-token pass (every q/k/v/out/fc1/fc2 linear a BSI op) inside an initialised
     process group; returns the measurements as a dict (max over ranks, CUDA events)."""
     import torch
@@ -416,7 +416,7 @@ def measure_opt(workload, steps, warmup, e2e_steps, rank, world, local_rank, opt
         # fused QKV key set, head-sharded attention, token-sharded residual stream, packed int8 exchanges
         from bsipytorch_b200.opt_tp import build_opt_tp
         model = build_opt_tp(workload, dtype=dtype, device=dev, seed=0, rank=rank, world=world,
-                             exchange=exchange, push=push, microbatches=microbatches)
+                             exchange=exchange, microbatches=microbatches, fuse_ln=fuse_ln, check_status=False)
         graphed = bool(cuda_graph) and (world == 1 or model.exchange == "peer")
         if graphed:
             model.capture(spec["batch"], spec["seq"])
@@ -518,7 +518,7 @@ def run_opt(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     r = measure_opt(args.workload, args.steps, args.warmup, args.e2e_steps, rank, world, local_rank, args.opt_impl,
-                    args.exchange, args.push, args.microbatches, args.cuda_graph, args.kernel_split)
+                    args.exchange, args.microbatches, args.cuda_graph, args.kernel_split, bool(args.fuse_ln))
     if rank == 0:
         B, T, K, ms = r["B"], r["T"], r["K"], r["ms"]
         peaks = measured_peaks()
@@ -560,8 +560,8 @@ def main():
     ap.add_argument("--cuda-graph", type=int, default=1, help="tensor-parallel OPT: replay the decoder stack from a CUDA graph")
     ap.add_argument("--kernel-split", action="store_true",
                     help="OPT workloads: after the timed regions, print the device time per kernel of three steps to stderr")
-    ap.add_argument("--push", default="store", choices=["copy", "store"],
-                    help="peer exchange: int8 blocks pushed by copy engines, or stored to every rank by the pack kernel")
+    ap.add_argument("--fuse-ln", type=int, default=0,
+                    help="tensor-parallel OPT: residual add + LayerNorm + pack in one kernel (not bit-identical to torch's LayerNorm)")
     ap.add_argument("--microbatches", type=int, default=2, help="peer exchange: sequence groups run on streams of their own")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "collective"],
                     help="tensor-parallel OPT: peer-memory stores (default on GPUs) or NCCL collectives")
@@ -808,7 +808,7 @@ def main():
     opt_block = None
     if args.extras and args.workload == "fc1":
         try:
-            r = measure_opt("opt-6.7b", args.opt_steps, 3, 3, rank, world, local_rank, "tp", args.exchange, args.push,
+            r = measure_opt("opt-6.7b", args.opt_steps, 3, 3, rank, world, local_rank, "tp", args.exchange,
                             args.microbatches, args.cuda_graph)
             opt_block = {"tokens_per_s": r["B"] * r["T"] * r["K"] / (r["ms"] * 1e-3), "ms_per_step": r["ms"] / r["K"],
                          "steps": r["K"], "warmup": r["warmup"], "batch": r["B"], "seq": r["T"], "exchange": r["exchange"],

@@ -34,8 +34,6 @@ SIGNATURES = {
     "bsi_b200_linear_i8_requant": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _i32, _i32, _i32, _i32,
                                           _i32, _vp, _i64, _vp, _i64, _vp]),
     "bsi_b200_add_layernorm_pack": (_i32, [_vp, _vp, _vp, _vp, _f32, _i32, _i64, _i64, _vp, _i32, _i32, _i32, _vp, _i64, _i32, _vp, _i64, _vp]),
-    "bsi_b200_set_grid_caps": (_i32, [_i32, _i32]),
-    "bsi_b200_peer_copy_2d": (_i32, [_vp, _i64, _vp, _i64, _i64, _i64, _vp]),
     "bsi_b200_peer_alloc": (_i32, [_i64, _vp, _vp]),
     "bsi_b200_peer_free": (_i32, [_vp]),
     "bsi_b200_peer_open": (_i32, [_vp, _vp]),

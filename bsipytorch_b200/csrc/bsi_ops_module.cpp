@@ -654,14 +654,6 @@ void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t
                  "bsi_b200_quantize_pack_multi");
 }
 
-// Copy-engine push of a [height, width_bytes] block between device addresses (own or peer mappings).
-void peer_copy_2d(int64_t dst, int64_t dst_pitch, int64_t src, int64_t src_pitch, int64_t width_bytes, int64_t height) {
-    check_status(bsi_b200_peer_copy_2d(reinterpret_cast<void*>(static_cast<intptr_t>(dst)), dst_pitch,
-                                       reinterpret_cast<const void*>(static_cast<intptr_t>(src)), src_pitch, width_bytes,
-                                       height, current_stream()),
-                 "bsi_b200_peer_copy_2d");
-}
-
 // linear_from_packed whose rows are dealt out to the matrices at y_ptrs (rows_per_dst rows each, leading
 // dimension ldy, element type out_dtype); returns nothing, the destinations are the caller's buffers.
 void linear_from_packed_scatter(torch::Tensor q8, torch::Tensor scales, py::capsule keyset_cuda_cap,
@@ -871,15 +863,11 @@ PYBIND11_MODULE(bsi_ops, m) {
     m.def("peer_close", &peer_close, py::arg("ptr"));
     m.def("peer_barrier", &peer_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("timeout_ms") = 2000,
           "Bounded flag barrier over the ranks, enqueued on the current stream");
-    m.def("set_grid_caps", [](int dot_sms, int pack_blocks) { check_status(bsi_b200_set_grid_caps(dot_sms, pack_blocks), "bsi_b200_set_grid_caps"); },
-          py::arg("dot_sms"), py::arg("pack_blocks"), "Cap the SMs of the dot kernels / blocks of the pack kernels (0 = no cap)");
     m.def("linear_from_packed_requant", &linear_from_packed_requant, py::arg("q8"), py::arg("scales"),
           py::arg("keyset_cuda_cap"), py::arg("bias"), py::arg("decimal_places"), py::arg("layer_dtype"), py::arg("relu"),
           py::arg("q8_ptrs"), py::arg("ld8"), py::arg("scale_ptrs"), py::arg("scale_ld"));
     m.def("add_layernorm_pack", &add_layernorm_pack, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("bias"),
           py::arg("eps"), py::arg("q8_ptrs"), py::arg("ld8"), py::arg("scale_ptrs"), py::arg("scale_ld"), py::arg("decimal_places"));
-    m.def("peer_copy_2d", &peer_copy_2d, py::arg("dst"), py::arg("dst_pitch"), py::arg("src"), py::arg("src_pitch"),
-          py::arg("width_bytes"), py::arg("height"));
     m.def("pack_queries_multi", &pack_queries_multi, py::arg("x2d"), py::arg("q8_ptrs"), py::arg("ld8"),
           py::arg("scale_ptrs"), py::arg("scale_ld"), py::arg("decimal_places"));
     m.def("linear_from_packed_scatter", &linear_from_packed_scatter, py::arg("q8"), py::arg("scales"),

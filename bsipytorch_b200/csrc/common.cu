@@ -16,13 +16,6 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
-// Optional caps on the grids of the persistent kernels (0 = none), process-wide.
-static int g_dot_sm_cap = 0;
-static int g_pack_block_cap = 0;
-
-int dot_sm_cap() { return g_dot_sm_cap; }
-int pack_block_cap() { return g_pack_block_cap; }
-
 bool pdl_enabled() {
     static int cached = -1;
     if (cached < 0) {
@@ -86,10 +79,3 @@ extern "C" const char* bsi_b200_status_string(int status) {
 extern "C" const char* bsi_b200_last_error(void) { return bsi::g_err; }
 
 extern "C" int bsi_b200_version(void) { return BSI_B200_VERSION; }
-
-extern "C" int bsi_b200_set_grid_caps(int dot_sms, int pack_blocks) {
-    if (dot_sms < 0 || pack_blocks < 0) return bsi::fail(BSI_ERR_INVALID, "set_grid_caps: negative cap");
-    bsi::g_dot_sm_cap = dot_sms;
-    bsi::g_pack_block_cap = pack_blocks;
-    return BSI_OK;
-}

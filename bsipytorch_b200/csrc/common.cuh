@@ -39,10 +39,6 @@ inline int check_launch(const char* what) {
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
-// Caps set through bsi_b200_set_grid_caps (0 = none): SMs the dot kernel may occupy, blocks of a pack launch.
-int dot_sm_cap();
-int pack_block_cap();
-
 // 0 when the current device is sm_100 class, an error code otherwise.
 int require_sm100();
 

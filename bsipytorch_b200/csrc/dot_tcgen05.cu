@@ -478,7 +478,6 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
         if (dev >= 0 && dev < 64) max_clusters[dev] = resident;
     }
     int pairs = tiles_total < resident ? tiles_total : resident;
-    if (dot_sm_cap() > 1 && pairs > dot_sm_cap() / 2) pairs = dot_sm_cap() / 2;   // leave SMs to concurrent streams
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT, REQ>, ma, mb, vector_store, qs,
                                     qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter, requant));

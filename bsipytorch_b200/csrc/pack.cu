@@ -779,7 +779,6 @@ int launch_chunk_fast(const T* x, const ChunkArgs& a) {
     if (resident <= 0) return BSI_ERR_CUDA;
     int64_t blocks = (a.rows * a.chunks + 7) / 8;
     blocks = blocks < resident ? blocks : resident;
-    if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();
     FastGeom g;
     g.total = static_cast<uint32_t>(a.rows * a.chunks);
     g.chunks = static_cast<uint32_t>(a.chunks);
@@ -925,7 +924,6 @@ extern "C" int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t ro
         if (resident <= 0) return BSI_ERR_CUDA;                                                             \
         int64_t blocks = (rows * chunks + 7) / 8;                                                           \
         blocks = blocks < resident ? blocks : resident;                                                     \
-        if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();                   \
         quantize_pack_multi_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                   \
             static_cast<const T*>(x), static_cast<uint32_t>(rows * chunks), static_cast<uint32_t>(chunks),  \
             static_cast<uint32_t>(ldx), static_cast<uint32_t>(ld8), static_cast<uint32_t>(scale_ld), dec_scale, \
@@ -982,7 +980,6 @@ extern "C" int bsi_b200_add_layernorm_pack(const void* x, const void* delta, con
     }
     const int cpw = static_cast<int>((chunks + 7) / 8);   // chunks per warp, 8 warps
     int64_t blocks = rows;   // one block per row; the kernel's row loop only matters under a block cap
-    if (pack_block_cap() > 0 && blocks > pack_block_cap()) blocks = pack_block_cap();
 #define BSI_LAUNCH_ALP(T, CPW_)                                                                                   \
     add_layernorm_pack_kernel<T, CPW_><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(                       \
         static_cast<const T*>(x), static_cast<const T*>(delta), static_cast<const T*>(gamma),                    \

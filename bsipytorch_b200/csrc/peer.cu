@@ -137,21 +137,3 @@ extern "C" int bsi_b200_peer_barrier(uint32_t* const* flags, int rank, int n, in
         t, rank, n, static_cast<unsigned long long>(timeout_ms) * 1000000ull);
     return check_launch("peer_barrier launch");
 }
-
-extern "C" int bsi_b200_peer_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
-                                     int64_t width_bytes, int64_t height, bsi_stream_t stream_) {
-    using namespace bsi;
-    if (width_bytes < 0 || height < 0 || dst_pitch < width_bytes || src_pitch < width_bytes)
-        return fail(BSI_ERR_INVALID, "peer_copy_2d: bad extent / pitch");
-    if (width_bytes == 0 || height == 0) return BSI_OK;
-    if (dst == nullptr || src == nullptr) return fail(BSI_ERR_INVALID, "peer_copy_2d: null pointer");
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if (dst_pitch == width_bytes && src_pitch == width_bytes) {
-        BSI_CUDA_TRY(cudaMemcpyAsync(dst, src, static_cast<size_t>(width_bytes * height), cudaMemcpyDeviceToDevice, stream));
-    } else {
-        BSI_CUDA_TRY(cudaMemcpy2DAsync(dst, static_cast<size_t>(dst_pitch), src, static_cast<size_t>(src_pitch),
-                                       static_cast<size_t>(width_bytes), static_cast<size_t>(height),
-                                       cudaMemcpyDeviceToDevice, stream));
-    }
-    return BSI_OK;
-}

@@ -87,10 +87,8 @@ class PeerExchange:
     A region is rewritten only after at least one barrier that follows its last reader on every rank,
     so one copy of each is enough."""
 
-    def __init__(self, m, rank, world, group, Q, H, Fd, dtype, device, timeout_ms=30000, push="store"):
+    def __init__(self, m, rank, world, group, Q, H, Fd, dtype, device, timeout_ms=30000):
         self.m, self.rank, self.world, self.timeout_ms = m, rank, world, int(timeout_ms)
-        self.rotate = True
-        self.push = push      # "copy": copy engines move the int8 blocks; "store": the pack kernel stores to every rank
         self.Q, self.H, self.F, self.Qn = Q, H, Fd, Q // world
         esz = torch.empty(0, dtype=dtype).element_size()
         self.esz = esz
@@ -125,22 +123,14 @@ class PeerExchange:
 
     def pack_to_all(self, x, dp, q8_name, sc_name, q8_off, sc_off, ld8, scale_ld, height):
         """Packs x and leaves its int8 image at byte offset q8_off of region q8_name (row pitch ld8) and its
-        chunk scales at byte offset sc_off of sc_name (scale_ld floats per row) on every rank, then passes
-        the barrier. The scales always leave from the pack kernel; the int8 block either too ("store") or
-        lands in the own buffer and is pushed to each peer by a copy engine ("copy")."""
+        chunk scales at byte offset sc_off of sc_name (scale_ld floats per row) on every rank -- the pack kernel
+        stores each packed unit to all of them -- then passes the barrier."""
         q8_ptrs, sc_ptrs = self.ptrs(q8_name, q8_off), self.ptrs(sc_name, sc_off)
         g, G = self.rank, self.world
-        if self.push == "store":
-            # the kernel walks its destinations in list order: start each rank at its successor, so that at any
-            # moment the ranks write to different peers instead of all converging on the same one
-            order = [(g + 1 + k) % G for k in range(G)] if self.rotate else list(range(G))
-            self.m.pack_queries_multi(x, [q8_ptrs[r] for r in order], ld8, [sc_ptrs[r] for r in order], scale_ld, dp)
-        else:
-            self.m.pack_queries_multi(x, [q8_ptrs[g]], ld8, sc_ptrs, scale_ld, dp)
-            width = x.shape[1]
-            for k in range(1, G):                      # start with the next rank: the pushes fan out evenly
-                r = (g + k) % G
-                self.m.peer_copy_2d(q8_ptrs[r], ld8, q8_ptrs[g], ld8, width, height)
+        # the kernel walks its destinations in list order: start each rank at its successor, so that at any
+        # moment the ranks write to different peers instead of all converging on the same one
+        order = [(g + 1 + k) % G for k in range(G)]
+        self.m.pack_queries_multi(x, [q8_ptrs[r] for r in order], ld8, [sc_ptrs[r] for r in order], scale_ld, dp)
         self.barrier()
 
     def barrier(self):
@@ -343,10 +333,16 @@ class TPOPTForCausalLM(nn.Module):
     """OPT with tensor-parallel BSI decoder layers; embeddings, final LayerNorm and lm_head are replicated."""
 
     def __init__(self, cfg: OPTConfig, rank=0, world=1, group=None, ops=None, dtype=torch.float16, device="cuda",
-                 exchange="auto", push="store", microbatches=2, fuse_ln=False):
+                 exchange="auto", microbatches=2, fuse_ln=False, peer_timeout_ms=30000, check_status=True):
         super().__init__()
         self.config, self.rank, self.world, self.group, self.dtype = cfg, rank, world, group, dtype
-        self.push, self.microbatches = push, int(microbatches)
+        self.microbatches = int(microbatches)
+        self.peer_timeout_ms = int(peer_timeout_ms)
+        # After every forward / next_token the device status word is read (this synchronises the device): a bounded
+        # wait that gave up (a peer that never arrived: 64 + its rank) or a re-quantised chunk holding inf / NaN (48)
+        # raises instead of returning values computed from stale or zeroed buffers. Loops that time the forward set
+        # this to False and read the status once at the end.
+        self.check_status = bool(check_status)
         self.ops = ops if ops is not None else BsiDeviceOps()
         if exchange not in ("auto", "peer", "collective"):
             raise ValueError("exchange must be auto, peer or collective")
@@ -375,7 +371,7 @@ class TPOPTForCausalLM(nn.Module):
 
     def _micro(self, B, T):
         """Number of micro-batches for a [B, T] input: with peer exchange the batch is split into groups of
-        sequences that run on streams of their own, so that one group's copy-engine pushes and barriers
+        sequences that run on streams of their own, so that one group's exchange stores and barriers
         overlap the other's kernels."""
         M = self.microbatches if (self.world > 1 and self.exchange == "peer") else 1
         while M > 1 and (B % M != 0 or ((B // M) * T // self.world) % 32 != 0):
@@ -486,31 +482,50 @@ class TPOPTForCausalLM(nn.Module):
             if (Q // self.world) % 32 != 0:
                 raise ValueError("peer exchange needs a multiple of 32 tokens per rank")
             px = PeerExchange(self.ops.m, self.rank, self.world, self.group, Q, self.config.hidden_size,
-                              self.config.ffn_dim, self.dtype, device, push=self.push)
+                              self.config.ffn_dim, self.dtype, device, timeout_ms=self.peer_timeout_ms)
             self._px[slot] = px
         return px
 
+    def _raise_on_device_status(self):
+        if not (self.check_status and isinstance(self.ops, BsiDeviceOps)):
+            return
+        status = int(self.ops.m.device_status())
+        if status == 0:
+            return
+        if status >= 64:
+            what = f"rank {status - 64} never arrived at a peer barrier within {self.peer_timeout_ms} ms"
+        elif status == 48:
+            what = "a re-quantised chunk held inf, NaN or a value beyond the exact range and was stored as zeros"
+        else:
+            what = "a bounded wait inside a dot kernel gave up"
+        raise RuntimeError(f"BSI device status {status} on rank {self.rank}: {what}; this forward's values are not valid")
+
     @torch.no_grad()
     def forward(self, input_ids):
-        return F.linear(self.hidden_states(input_ids), self.embed_tokens.weight)
+        out = F.linear(self.hidden_states(input_ids), self.embed_tokens.weight)
+        self._raise_on_device_status()
+        return out
 
     @torch.no_grad()
     def next_token(self, input_ids):
         """Last-position argmax, the reference's accuracy statistic (benchmark_performance_bsi.py:209-212)."""
-        return F.linear(self.hidden_states(input_ids)[:, -1, :], self.embed_tokens.weight).argmax(dim=-1)
+        tok = F.linear(self.hidden_states(input_ids)[:, -1, :], self.embed_tokens.weight).argmax(dim=-1)
+        self._raise_on_device_status()
+        return tok
 
 
 @torch.no_grad()
 def build_opt_tp(name="opt-6.7b", dtype=torch.float16, device="cuda", seed=0, decimal_places=2,
                  compress_threshold=0.5, rank=0, world=1, group=None, ops=None, exchange="auto",
-                 push="store", microbatches=2, fuse_ln=False):
+                 microbatches=2, fuse_ln=False, peer_timeout_ms=30000, check_status=True):
     """Random-init tensor-parallel OPT. Draws every parameter from the generator `build_opt_bsi` uses for
     it (seeded by the parameter's position in the sorted HF names), so the two models hold the same
     weights, and builds the keys layer by layer so that the dense weights never sit in memory at once."""
     cfg = CONFIGS[name] if isinstance(name, str) else name
     if ops is None:
         ops = BsiDeviceOps(decimal_places, compress_threshold)
-    model = TPOPTForCausalLM(cfg, rank, world, group, ops, dtype, device, exchange, push, microbatches, fuse_ln)
+    model = TPOPTForCausalLM(cfg, rank, world, group, ops, dtype, device, exchange, microbatches, fuse_ln, peer_timeout_ms,
+                             check_status)
     H, Fd, L = cfg.hidden_size, cfg.ffn_dim, cfg.num_hidden_layers
     shapes = {"model.decoder.embed_tokens.weight": (cfg.vocab_size, H),
               "model.decoder.embed_positions.weight": (cfg.max_position_embeddings + 2, H),

@@ -169,19 +169,11 @@ int bsi_b200_linear_i8_requant(const int8_t* a8, int64_t lda, const float* qs, i
                                int n_dst, int8_t* const* q8_dst, int64_t ld8,
                                float* const* scale_dst, int64_t scale_ld, bsi_stream_t stream);
 
-/* Process-wide caps on the grids of the persistent kernels, 0 = none (the default): dot_sms limits
- * the SMs the dot / linear kernels occupy (pairs of CTAs, so the even part counts), pack_blocks the
- * blocks of a pack launch. With several streams in flight (micro-batches of the tensor-parallel
- * layer) the SMs left free run one stream's exchange kernels while another's dot computes. */
-int bsi_b200_set_grid_caps(int dot_sms, int pack_blocks);
-
 /* Chunk-mode quantise + pack of activations (int8 image and chunk scales only) written to several
  * places at once: the int8 image to q8_dst[i] + row * ld8 + col for i < n_q8_dst, the chunk scales to
  * scale_dst[i] + row * scale_ld + chunk for i < n_scale_dst. The pointers already include the column /
- * row offset of this rank's block inside each destination matrix; they may be peer mappings (the small
- * scale arrays usually go to every rank from the kernel, the int8 image either too or only to the
- * local buffer, to be pushed by bsi_b200_peer_copy_2d). D must be a multiple of 256, x 16-byte
- * aligned with ldx * sizeof(x) % 16 == 0. */
+ * row offset of this rank's block inside each destination matrix; they may be peer mappings. D must be a
+ * multiple of 256, x 16-byte aligned with ldx * sizeof(x) % 16 == 0. */
 int bsi_b200_quantize_pack_multi(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
                                  int decimal_places, int bits, int n_q8_dst, int8_t* const* q8_dst,
                                  int64_t ld8, int n_scale_dst, float* const* scale_dst, int64_t scale_ld,
@@ -200,12 +192,6 @@ int bsi_b200_add_layernorm_pack(const void* x, const void* delta, const void* ga
                                 int decimal_places, int bits, int n_q8_dst, int8_t* const* q8_dst,
                                 int64_t ld8, int n_scale_dst, float* const* scale_dst, int64_t scale_ld,
                                 bsi_stream_t stream);
-
-/* Copies a block of `height` rows of `width_bytes` bytes between device buffers (either may be a peer
- * mapping) with the copy engines, enqueued on `stream`: cudaMemcpy2DAsync, device to device. Used to
- * push a rank's block of packed activations to its peers without occupying SMs. */
-int bsi_b200_peer_copy_2d(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch,
-                          int64_t width_bytes, int64_t height, bsi_stream_t stream);
 
 /* bsi_b200_linear_i8_act whose output rows are dealt out to n_dst matrices: row q goes to
  * y_dst[q / rows_per_dst] at local row q % rows_per_dst, column r, leading dimension ldy (the

@@ -54,7 +54,7 @@ def test_sharded_opt_equals_single_gpu(tmp_path):
     assert res["finite"] and res["equal"]
 
 
-def _tp_worker(rank, world, port, out_path, exchange, push, microbatches):
+def _tp_worker(rank, world, port, out_path, exchange, microbatches):
     import torch.distributed as dist
 
     from bsipytorch_b200 import opt
@@ -68,7 +68,7 @@ def _tp_worker(rank, world, port, out_path, exchange, push, microbatches):
                             max_position_embeddings=128, name="tiny")
         from bsipytorch_b200 import bsi_ops
         model = build_opt_tp(cfg, dtype=torch.float16, device=f"cuda:{rank}", seed=11, rank=rank, world=world,
-                             exchange=exchange, push=push, microbatches=microbatches)
+                             exchange=exchange, microbatches=microbatches, peer_timeout_ms=5000)
         ids = torch.randint(0, 512, (4, 32), generator=torch.Generator().manual_seed(2)).to(f"cuda:{rank}")
         hidden = model.hidden_states(ids)
         tokens = model.next_token(ids)
@@ -89,15 +89,14 @@ def _tp_worker(rank, world, port, out_path, exchange, push, microbatches):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("exchange,push,microbatches", [("peer", "copy", 2), ("peer", "store", 1), ("peer", "copy", 1),
-                                                        ("collective", "copy", 1)])
-def test_tensor_parallel_opt_equals_single_gpu(tmp_path, exchange, push, microbatches):
+@pytest.mark.parametrize("exchange,microbatches", [("peer", 2), ("peer", 1), ("collective", 1)])
+def test_tensor_parallel_opt_equals_single_gpu(tmp_path, exchange, microbatches):
     """Head-sharded attention runs the same kernel per head on fewer heads; everything else is the same
     arithmetic per element, so the hidden states agree to the last bit (a tolerance of one fp16 ulp of the
     O(1) LayerNorm outputs covers an attention kernel that tiles differently for a different head count)."""
     world = 2
     out_path = str(tmp_path / "tp.pt")
-    mp.spawn(_tp_worker, args=(world, _free_port(), out_path, exchange, push, microbatches), nprocs=world, join=True)
+    mp.spawn(_tp_worker, args=(world, _free_port(), out_path, exchange, microbatches), nprocs=world, join=True)
     res = torch.load(out_path)
     assert res["status"] == 0, "a bounded device-side wait gave up"
     assert res["finite"] and res["tokens_equal"] and res["graph_equal"]
