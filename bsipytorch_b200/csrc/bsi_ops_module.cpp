@@ -3,11 +3,12 @@
 // top of the bsi_b200 C ABI. Host logic only: tensors are allocated here, every kernel lives in
 // libbsi_b200.so.
 //
-// Mode: the fixed-bit block-floating path of the reference (queries BSI_FIXED_BITS_QUERIES bits,
+// Modes: the fixed-bit block-floating path of the reference (queries BSI_FIXED_BITS_QUERIES bits,
 // default 7, with per-256-element chunk scales when BSI_FIXED_CHUNK_SCALE != 0, default on; keys
 // BSI_FIXED_BITS_KEYS bits, default 6, per-row scale). The reference needs those variables to be
-// set to reach this path (its README's fixed76 recipe); here they are the defaults. The
-// variable-slice mode (bits = 0), which needs the un-vendored bsiCPP key builder, is rejected.
+// set to reach this path (its README's fixed76 recipe); here they are the defaults. Setting a
+// variable to 0 selects the reference's variable-slice mode for that side: the decimal integers
+// are sliced without a shift and the slice count follows from the data (pack_variable below).
 #include <torch/extension.h>
 #include <pybind11/stl.h>
 
@@ -17,6 +18,9 @@
 
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
+#include <filesystem>
+#include <fstream>
 #include <memory>
 #include <string>
 #include <unordered_map>
@@ -38,9 +42,7 @@ int fixed_bits(const char* specific, int fallback) {
     int v = fallback;
     if (const char* s = std::getenv(specific)) v = std::atoi(s);
     else if (const char* g = std::getenv("BSI_FIXED_BITS")) v = std::atoi(g);
-    TORCH_CHECK(v > 0, specific, "=0 selects the reference's variable-slice mode, which this build does not provide "
-                "(it depends on the bsiCPP key builder); use fixed bits in [2, 8]");
-    TORCH_CHECK(v >= 2 && v <= 8, specific, " must be in [2, 8] for the int8 tensor-core path, got ", v);
+    TORCH_CHECK(v == 0 || (v >= 2 && v <= 8), specific, " must be 0 (variable-slice mode) or in [2, 8], got ", v);
     return v;
 }
 int bits_queries() { return fixed_bits("BSI_FIXED_BITS_QUERIES", 7); }
@@ -102,6 +104,9 @@ struct PackedBatch {
     at::Tensor scales;         // [rows, chunks] (chunk mode) or [rows] (row mode) float32: 2^shift
     at::Tensor q8;             // [rows, ld8] int8
     bool chunk_mode = false;
+    bool variable = false;     // variable-slice mode: no shift, q8 holds the integers (their low digit when q8_hi is set)
+    at::Tensor q8_hi;          // [rows, ld8] int8: v = 128 * q8_hi + q8 (only when some |v| > 127)
+    std::vector<int> row_slices;   // variable-slice keys: slice count of every row (bit_width(max|v|) + 2)
     int S = 0;
     int W = 0;
     int64_t rows = 0;
@@ -201,10 +206,94 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
     return b;
 }
 
+int variable_slices(uint64_t max_abs) {
+    // bsi_vector_cuda.cpp:746-754: bit_width(max |v|) + 2 slices, 2 when everything is zero, at most 64
+    int width = 0;
+    while (width < 64 && (max_abs >> width) != 0) ++width;
+    return max_abs ? std::min(64, std::max(1, width) + 2) : 2;
+}
+
+// Variable-slice mode (the reference without BSI_FIXED_BITS*: bsi_vector_cuda.cpp:1086-1166 for query batches,
+// bsi_cuda.cpp:912-1007 for keys, whose per-row builder lives in bsiCPP): v = half_away(x * 10^dp), no shift.
+// Queries: one slice count for the batch, from the largest |v|; a row uses two's-complement slice weights when it
+// holds a negative value, unsigned ones otherwise. Keys: every row has its own count (kept in row_slices for the
+// stats); they are stored at the width of the widest row, sign-extended, which leaves every value unchanged.
+// The tensor-core dot reads the integers as signed 8-bit digits: queries up to two digits (|v| < 2^14), keys one
+// (|v| <= 127); anything larger is refused rather than computed some other way.
+PackedBatch pack_variable(const at::Tensor& input, int decimal_places, bool for_keys) {
+    TORCH_CHECK(input.dim() == 2, "expects 2D tensor [rows, d]");
+    const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
+    at::Tensor x = input.detach();
+    if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
+        x = x.to(at::kFloat);
+    x = x.to(dev, /*non_blocking=*/false).contiguous();
+    PackedBatch b;
+    b.variable = true;
+    b.rows = x.size(0);
+    b.d = x.size(1);
+    b.W = b.d > 0 ? static_cast<int>((b.d + 63) / 64) : 1;
+    b.chunks = (b.d + 255) / 256;
+    b.decimals = decimal_places;
+    b.chunk_mode = false;
+    auto opt = [&](at::ScalarType t) { return at::TensorOptions().dtype(t).device(dev); };
+    at::Tensor absmax = at::zeros({b.rows}, opt(at::kLong));
+    at::Tensor negative = at::zeros({b.rows}, opt(at::kInt));
+    if (b.rows > 0 && b.d > 0)
+        check_status(bsi_b200_decimal_absmax(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places,
+                                             reinterpret_cast<uint64_t*>(absmax.data_ptr<int64_t>()), negative.data_ptr<int>(),
+                                             current_stream()),
+                     "bsi_b200_decimal_absmax");
+    at::Tensor absmax_h = absmax.to(at::kCPU);     // the reference synchronises here too (.item(), bsi_vector_cuda.cpp:1093-1096)
+    uint64_t max_abs = 0;
+    b.row_slices.resize(static_cast<size_t>(b.rows));
+    for (int64_t r = 0; r < b.rows; ++r) {
+        const uint64_t m = static_cast<uint64_t>(absmax_h.data_ptr<int64_t>()[r]);
+        max_abs = std::max(max_abs, m);
+        b.row_slices[static_cast<size_t>(r)] = variable_slices(m);
+    }
+    b.S = variable_slices(max_abs);
+    if (!for_keys) std::fill(b.row_slices.begin(), b.row_slices.end(), b.S);
+    TORCH_CHECK(max_abs <= (for_keys ? 127ull : 16383ull), "variable-slice mode: |value * 10^decimal_places| reaches ", max_abs,
+                for_keys ? "; keys beyond 127 (8 bits) are not supported" : "; queries beyond 16383 (two 8-bit digits) are not supported",
+                " by the tensor-core dot");
+    const int64_t ld8 = std::max<int64_t>(b.chunks, 1) * 256;
+    b.words = at::zeros({b.rows, b.S, b.W}, opt(at::kLong));
+    b.q8 = at::empty({b.rows, ld8}, opt(at::kChar));
+    const bool two_digits = max_abs > 127;
+    if (two_digits) b.q8_hi = at::empty({b.rows, ld8}, opt(at::kChar));
+    if (b.rows > 0 && b.d > 0) {
+        check_status(bsi_b200_pack_plain(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, b.S,
+                                         reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()), b.q8.data_ptr<int8_t>(),
+                                         two_digits ? b.q8_hi.data_ptr<int8_t>() : nullptr, ld8, current_stream()),
+                     "bsi_b200_pack_plain");
+    } else {
+        b.q8.zero_();
+    }
+    b.scales = at::ones({b.rows}, opt(at::kFloat));
+    // +2^i everywhere, or with the top slice negative for rows that hold a negative value (bsi_vector_cuda.cpp:1156-1162)
+    std::vector<float> wu(static_cast<size_t>(b.S)), wt(static_cast<size_t>(b.S));
+    for (int i = 0; i < b.S; ++i) {
+        wu[static_cast<size_t>(i)] = std::ldexp(1.0f, i);
+        wt[static_cast<size_t>(i)] = (i == b.S - 1) ? -std::ldexp(1.0f, i) : std::ldexp(1.0f, i);
+    }
+    at::Tensor unsigned_w = torch::tensor(wu, torch::dtype(torch::kFloat32)).to(dev).unsqueeze(0);
+    at::Tensor twos_w = torch::tensor(wt, torch::dtype(torch::kFloat32)).to(dev).unsqueeze(0);
+    b.slice_weights = at::where(negative.ne(0).unsqueeze(1), twos_w, unsigned_w).contiguous();
+    return b;
+}
+
+void require_fixed_queries(const char* what) {
+    TORCH_CHECK(bits_queries() > 0, what, " needs the fixed-bit query mode (BSI_FIXED_BITS_QUERIES in [2, 8])");
+}
+
 // Queries get chunk scales when enabled and the word count allows 256-bit chunks
 // (bsi_vector_cuda.cpp:980-994).
 PackedBatch pack_queries(const at::Tensor& q2d, int decimal_places, bool lean = false) {
     const int bits = bits_queries();
+    if (bits == 0) {
+        g_last_quantize_ns = g_last_pack_ns = g_last_total_ns = 0;
+        return pack_variable(q2d, decimal_places, /*for_keys=*/false);
+    }
     const int64_t d = q2d.size(1);
     const int W = d > 0 ? static_cast<int>((d + 63) / 64) : 1;
     const bool chunk = chunk_scale_enabled() && (W % 4 == 0);
@@ -228,10 +317,16 @@ size_t batch_mem_bytes(const PackedBatch& b) {
 py::tuple build_bsi_keys_cuda(torch::Tensor K, int decimalPlaces, float compress_threshold) {
     TORCH_CHECK(K.dim() == 2, "K must be 2D [num_keys, d]");
     auto* holder = new PrebuiltBSIKeysCUDA();
-    holder->b = pack(K, decimalPlaces, bits_keys(), /*chunk_mode=*/false, /*profile=*/false);
+    const int kbits = bits_keys();
+    holder->b = kbits == 0 ? pack_variable(K, decimalPlaces, /*for_keys=*/true)
+                           : pack(K, decimalPlaces, kbits, /*chunk_mode=*/false, /*profile=*/false);
     holder->num_keys = K.size(0);
     holder->threshold = compress_threshold;
-    const uint64_t total_mem_bytes = static_cast<uint64_t>(holder->b.words.numel() * holder->b.words.element_size());
+    uint64_t total_mem_bytes = static_cast<uint64_t>(holder->b.words.numel() * holder->b.words.element_size());
+    if (holder->b.variable) {   // what the reference's per-row vectors would hold: each row its own slice count
+        total_mem_bytes = 0;
+        for (int sb : holder->b.row_slices) total_mem_bytes += static_cast<uint64_t>(sb) * holder->b.W * 8;
+    }
     py::capsule cap(holder, "PrebuiltBSIKeysCUDA", [](PyObject* c) {
         delete reinterpret_cast<PrebuiltBSIKeysCUDA*>(PyCapsule_GetPointer(c, "PrebuiltBSIKeysCUDA"));
     });
@@ -275,8 +370,10 @@ py::tuple build_bsi_query_cuda(torch::Tensor q, int decimalPlaces, float compres
     TORCH_CHECK(q.dim() == 1, "q must be 1D [d]");
     (void)compress_threshold;
     auto parent = std::make_shared<PackedBatch>(
-        pack(q.unsqueeze(0), decimalPlaces, bits_queries(), /*chunk_mode=*/false, /*profile=*/false));
-    const bool has_negative = q.numel() > 0 && parent->q8.lt(0).any().item<bool>();
+        bits_queries() == 0 ? pack_variable(q.unsqueeze(0), decimalPlaces, /*for_keys=*/false)
+                            : pack(q.unsqueeze(0), decimalPlaces, bits_queries(), /*chunk_mode=*/false, /*profile=*/false));
+    const bool has_negative = q.numel() > 0 && (parent->variable ? parent->slice_weights.lt(0).any().item<bool>()
+                                                                 : parent->q8.lt(0).any().item<bool>());
     py::capsule cap = row_capsule(parent, 0, has_negative);
     const uint64_t mem = static_cast<uint64_t>(parent->words.numel() * parent->words.element_size());
     return py::make_tuple(cap, mem, parent->S, parent->W);
@@ -336,8 +433,10 @@ at::Tensor ewah_decode(const EwahStream& e, int64_t W) {
 py::tuple build_bsi_query_cuda_hybrid(torch::Tensor q, int decimalPlaces, double compress_threshold) {
     TORCH_CHECK(q.dim() == 1, "q must be 1D [d]");
     auto parent = std::make_shared<PackedBatch>(
-        pack(q.unsqueeze(0), decimalPlaces, bits_queries(), /*chunk_mode=*/false, /*profile=*/false));
-    const bool has_negative = q.numel() > 0 && parent->q8.lt(0).any().item<bool>();
+        bits_queries() == 0 ? pack_variable(q.unsqueeze(0), decimalPlaces, /*for_keys=*/false)
+                            : pack(q.unsqueeze(0), decimalPlaces, bits_queries(), /*chunk_mode=*/false, /*profile=*/false));
+    const bool has_negative = q.numel() > 0 && (parent->variable ? parent->slice_weights.lt(0).any().item<bool>()
+                                                                 : parent->q8.lt(0).any().item<bool>());
     auto words2d = parent->words.view({parent->S, parent->W});
     EwahStream e = ewah_encode(words2d, compress_threshold);
     parent->words = ewah_decode(e, parent->W).view({1, parent->S, parent->W});
@@ -375,7 +474,25 @@ py::tuple run_dot(const PackedBatch& qb, const PrebuiltBSIKeysCUDA& keys, bool w
     }
     const int engine = engine_from_env();
     const int64_t qs_stride = qb.chunk_mode ? qb.chunks : 0;
-    if (engine == BSI_ENGINE_BMMA) {
+    if (qb.variable || keys.b.variable) {
+        TORCH_CHECK(engine != BSI_ENGINE_BMMA, "the b1 mma.sync engine reads fixed-bit slices; variable-slice operands use the int8 engines");
+        TORCH_CHECK(!want_iacc, "the per-chunk accumulator dump is defined for the fixed-bit mode");
+    }
+    if (qb.variable && qb.q8_hi.defined()) {
+        // Two-digit queries, v = 128 * hi + lo: one exact integer dot per digit with unit scales, then
+        // (128 * I_hi + I_lo) * bw0[r] * scale_inv. Every intermediate is an integer below 2^24 times a power of two
+        // wherever the reference's own float32 accumulation (bsi_cuda_kernels_dot.cuh:597-654) is exact, so the two agree.
+        at::Tensor out_hi = at::empty({Q, R}, fopt);
+        for (int digit = 0; digit < 2; ++digit) {
+            const at::Tensor& a8 = digit == 0 ? qb.q8 : qb.q8_hi;
+            at::Tensor& dst = digit == 0 ? out : out_hi;
+            check_status(bsi_b200_dot_i8(a8.data_ptr<int8_t>(), a8.size(1), qb.scales.data_ptr<float>(), 0,
+                                         keys.b.q8.data_ptr<int8_t>(), keys.b.q8.size(1), keys.b.scales.data_ptr<float>(),
+                                         Q, R, qb.chunks, 1.0f, dst.data_ptr<float>(), R, nullptr, engine, current_stream()),
+                         "bsi_b200_dot_i8");
+        }
+        out.add_(out_hi, 128.0f).mul_(static_cast<float>(scale_inv));
+    } else if (engine == BSI_ENGINE_BMMA) {
         check_status(bsi_b200_dot_words(reinterpret_cast<const uint64_t*>(qb.words.data_ptr<int64_t>()),
                                         qb.scales.data_ptr<float>(), qs_stride, qb.S, qb.W,
                                         reinterpret_cast<const uint64_t*>(keys.b.words.data_ptr<int64_t>()),
@@ -429,19 +546,25 @@ PackedBatch batch_from_list(const py::list& caps) {
     if (whole) return *p0;
     PackedBatch b;
     b.S = p0->S; b.W = p0->W; b.d = p0->d; b.chunks = p0->chunks; b.decimals = p0->decimals;
-    b.chunk_mode = p0->chunk_mode; b.rows = Q;
-    std::vector<at::Tensor> words, weights, scales, q8;
+    b.chunk_mode = p0->chunk_mode; b.rows = Q; b.variable = p0->variable;
+    bool any_hi = false;
+    for (int64_t i = 0; i < Q; ++i) any_hi = any_hi || rows[i]->parent->q8_hi.defined();
+    std::vector<at::Tensor> words, weights, scales, q8, q8_hi;
     for (int64_t i = 0; i < Q; ++i) {
         const auto& p = rows[i]->parent;
         TORCH_CHECK(p->W == b.W, "Word count mismatch across queries");
         TORCH_CHECK(p->decimals == b.decimals, "Decimal mismatch across queries not supported");
-        TORCH_CHECK(p->S == b.S, "Mixed slice counts across queries are not supported in fixed-bit mode");
+        TORCH_CHECK(p->S == b.S, "Mixed slice counts across queries are not supported");
+        TORCH_CHECK(p->variable == b.variable, "Mixed fixed-bit and variable-slice queries in the same group");
         TORCH_CHECK(p->chunk_mode == b.chunk_mode, "Mixed chunk-scale and non-chunk-scale queries in the same group");
         words.push_back(p->words[rows[i]->row]);
         weights.push_back(p->slice_weights[rows[i]->row]);
         scales.push_back(p->scales[rows[i]->row]);
         q8.push_back(p->q8[rows[i]->row]);
+        if (any_hi) q8_hi.push_back(p->q8_hi.defined() ? p->q8_hi[rows[i]->row] : at::zeros_like(p->q8[rows[i]->row]));
     }
+    if (any_hi) b.q8_hi = at::stack(q8_hi).contiguous();
+    b.row_slices.assign(static_cast<size_t>(Q), b.S);
     b.words = at::stack(words).contiguous();
     b.slice_weights = at::stack(weights).contiguous();
     b.scales = at::stack(scales).contiguous();
@@ -461,7 +584,13 @@ py::tuple batch_dot_product_multiquery_cuda_caps(py::list query_caps_list, py::c
 py::dict bsi_keys_cuda_stats(py::capsule keyset_cuda_cap) {
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     py::dict sb;
-    sb[py::int_(keys->b.S)] = py::int_(keys->num_keys);
+    if (keys->b.variable) {   // histogram of the per-row slice counts, as the reference groups its keys (bsi_cuda.cpp:956-999)
+        std::unordered_map<int, int64_t> hist;
+        for (int v : keys->b.row_slices) ++hist[v];
+        for (const auto& kv : hist) sb[py::int_(kv.first)] = py::int_(kv.second);
+    } else {
+        sb[py::int_(keys->b.S)] = py::int_(keys->num_keys);
+    }
     py::dict out;
     out["W"] = py::int_(keys->b.W);
     out["d"] = py::int_(keys->b.d);
@@ -504,7 +633,8 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
     const int engine = engine_from_env();
-    const bool fused = engine == BSI_ENGINE_AUTO || engine == BSI_ENGINE_TCGEN05;
+    // two-digit variable-slice queries need two dots and a combine: they take the unfused route below
+    const bool fused = (engine == BSI_ENGINE_AUTO || engine == BSI_ENGINE_TCGEN05) && bits_queries() > 0;
     PackedBatch qb = pack_queries(x2d, decimalPlaces, /*lean=*/fused);
     const int64_t Q = qb.rows, R = keys->num_keys;
     TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
@@ -546,6 +676,7 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
 // that a tensor-parallel layer can pack its own column block straight into the buffer the ranks
 // exchange. d must be a multiple of 256.
 void pack_queries_into(torch::Tensor x2d, torch::Tensor q8, torch::Tensor scales, int decimalPlaces) {
+    require_fixed_queries("pack_queries_into");
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [rows, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
@@ -636,6 +767,7 @@ void peer_barrier(std::vector<int64_t> flag_ptrs, int rank, int64_t timeout_ms) 
 // scale_ptrs[i] + 4 * (row * scale_ld + chunk).
 void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
                         int64_t scale_ld, int decimalPlaces) {
+    require_fixed_queries("pack_queries_multi");
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
     TORCH_CHECK(!q8_ptrs.empty() && !scale_ptrs.empty(), "destination lists must not be empty");
     check_clip();
@@ -696,6 +828,7 @@ void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::caps
                                 c10::optional<torch::Tensor> bias, int decimalPlaces, py::object layer_dtype, bool relu,
                                 std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
                                 int64_t scale_ld) {
+    require_fixed_queries("linear_from_packed_requant");
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
@@ -734,6 +867,7 @@ void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::caps
 at::Tensor add_layernorm_pack(torch::Tensor x, c10::optional<torch::Tensor> delta, torch::Tensor weight, torch::Tensor bias,
                               double eps, std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
                               int64_t scale_ld, int decimalPlaces) {
+    require_fixed_queries("add_layernorm_pack");
     TORCH_CHECK(x.dim() == 2 && x.is_cuda() && x.is_contiguous(), "x must be a contiguous 2D CUDA tensor");
     TORCH_CHECK(x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, "x must be float16 or bfloat16");
     TORCH_CHECK(weight.scalar_type() == x.scalar_type() && bias.scalar_type() == x.scalar_type() && weight.is_contiguous() &&
@@ -814,6 +948,185 @@ at::Tensor ewah_decode_words(torch::Tensor stream, torch::Tensor off, torch::Ten
     return ewah_decode(e, W);
 }
 
+// ---- keyset persistence ---------------------------------------------------------------------------
+// One file per key set, `<dir>/keyset.bsik`, holding what the dot needs in its stored form: the per-row scales and
+// the bit slices as EWAH / verbatim streams (the encoder of this library, with the key set's compress threshold).
+// It takes the place of the reference's save_keyset (bsiFunctions.cpp:792-808: one HybridBitmap file per slice, a
+// bsiCPP format) and of its checkpoint scripts, which store the dense weights and quantise again on every load
+// (benchmarks/export_bsi_checkpoint.py:57-87). Little-endian:
+//   0  char[8]  "BSIKEYS\0"      8  u32 version (1)      12 u32 header bytes (80)
+//   16 u64 num_keys   24 u64 d    32 u32 W   36 u32 bits  40 i32 decimal places   44 f32 compress threshold
+//   48 u64 stream words           56 u64 FNV-1a of the payload     64 u32 flags (bit 0: variable-slice keys)   68.. zero
+//   payload: f32 scale[num_keys] (2^shift of each row), i32 len[num_keys * bits] (encoded words per slice, in
+//   row-major slice order; a slice starts where the previous one ends), u64 stream[stream words]
+struct KeysetHeader {
+    char magic[8];
+    uint32_t version, header_bytes;
+    uint64_t num_keys, d;
+    uint32_t W, bits;
+    int32_t decimals;
+    float threshold;
+    uint64_t stream_words, checksum;
+    uint32_t flags, reserved0;
+    uint64_t reserved1;
+};
+static_assert(sizeof(KeysetHeader) == 80, "keyset header layout");
+
+uint64_t fnv1a(uint64_t h, const void* data, size_t n) {
+    const unsigned char* p = static_cast<const unsigned char*>(data);
+    for (size_t i = 0; i < n; ++i) {
+        h ^= p[i];
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+
+std::string keyset_path(const std::string& dir_or_file) {
+    const std::string suffix = ".bsik";
+    if (dir_or_file.size() > suffix.size() && dir_or_file.compare(dir_or_file.size() - suffix.size(), suffix.size(), suffix) == 0)
+        return dir_or_file;
+    return dir_or_file + "/keyset.bsik";
+}
+
+struct KeysetImage {
+    KeysetHeader h;
+    at::Tensor scales, len, stream;   // host tensors: float32 [R], int32 [R * bits], int64 [stream words]
+};
+
+KeysetImage encode_keyset(const PrebuiltBSIKeysCUDA& keys) {
+    const PackedBatch& b = keys.b;
+    TORCH_CHECK(!b.chunk_mode && b.words.defined(), "key sets carry one scale per row and their bit slices");
+    KeysetImage img;
+    EwahStream e = ewah_encode(b.words.view({b.rows * b.S, b.W}), keys.threshold);
+    img.scales = b.scales.to(at::kCPU).contiguous();
+    img.len = e.len.to(at::kCPU).contiguous();
+    img.stream = e.stream.to(at::kCPU).contiguous();
+    std::memset(&img.h, 0, sizeof(img.h));
+    std::memcpy(img.h.magic, "BSIKEYS", 8);
+    img.h.version = 1;
+    img.h.header_bytes = sizeof(KeysetHeader);
+    img.h.num_keys = static_cast<uint64_t>(b.rows);
+    img.h.d = static_cast<uint64_t>(b.d);
+    img.h.W = static_cast<uint32_t>(b.W);
+    img.h.bits = static_cast<uint32_t>(b.S);
+    img.h.decimals = b.decimals;
+    img.h.threshold = keys.threshold;
+    img.h.stream_words = static_cast<uint64_t>(e.total);
+    img.h.flags = b.variable ? 1u : 0u;
+    uint64_t c = 1469598103934665603ull;
+    c = fnv1a(c, img.scales.data_ptr(), img.scales.numel() * 4);
+    c = fnv1a(c, img.len.data_ptr(), img.len.numel() * 4);
+    c = fnv1a(c, img.stream.data_ptr(), img.stream.numel() * 8);
+    img.h.checksum = c;
+    return img;
+}
+
+// (bytes of the verbatim slices in device memory, bytes of the file): keyset_size_on_disk of the reference
+// (bsiFunctions.cpp:776-790) for a CUDA key set.
+py::tuple keyset_size_on_disk(py::capsule keyset_cuda_cap) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(keys != nullptr, "Invalid CUDA keys capsule");
+    KeysetImage img = encode_keyset(*keys);
+    const uint64_t disk = sizeof(KeysetHeader) + img.scales.numel() * 4 + img.len.numel() * 4 + img.stream.numel() * 8;
+    const uint64_t mem = static_cast<uint64_t>(keys->b.words.numel() * keys->b.words.element_size());
+    return py::make_tuple(mem, disk);
+}
+
+py::none save_keyset(py::capsule keyset_cuda_cap, const std::string& out_dir) {
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
+    TORCH_CHECK(keys != nullptr, "Invalid CUDA keys capsule");
+    KeysetImage img = encode_keyset(*keys);
+    const std::string path = keyset_path(out_dir);
+    if (path != out_dir) std::filesystem::create_directories(out_dir);
+    std::ofstream ofs(path, std::ios::binary | std::ios::trunc);
+    TORCH_CHECK(ofs.good(), "Failed to open file: ", path);
+    ofs.write(reinterpret_cast<const char*>(&img.h), sizeof(img.h));
+    ofs.write(static_cast<const char*>(img.scales.data_ptr()), img.scales.numel() * 4);
+    ofs.write(static_cast<const char*>(img.len.data_ptr()), img.len.numel() * 4);
+    ofs.write(static_cast<const char*>(img.stream.data_ptr()), img.stream.numel() * 8);
+    ofs.close();
+    TORCH_CHECK(ofs.good(), "Failed to write file: ", path);
+    return py::none();
+}
+
+// Reads a key set written by save_keyset onto the current CUDA device: decodes the slice streams, rebuilds the int8
+// image from the slices and returns what build_bsi_keys_cuda returns, without touching the dense weights.
+py::tuple load_keyset(const std::string& dir_or_file) {
+    const std::string path = keyset_path(dir_or_file);
+    std::ifstream ifs(path, std::ios::binary);
+    TORCH_CHECK(ifs.good(), "Failed to open file: ", path);
+    KeysetHeader h;
+    ifs.read(reinterpret_cast<char*>(&h), sizeof(h));
+    TORCH_CHECK(ifs.good() && std::memcmp(h.magic, "BSIKEYS", 8) == 0, path, " is not a BSI key set file");
+    TORCH_CHECK(h.version == 1 && h.header_bytes == sizeof(KeysetHeader), path, ": unsupported key set version ", h.version);
+    TORCH_CHECK(h.bits >= 2 && h.bits <= 8 && h.W >= 1 && h.W == (h.d + 63) / 64 && h.num_keys < (1ull << 40) &&
+                    h.stream_words <= h.num_keys * h.bits * (static_cast<uint64_t>(h.W) + 1),
+                path, ": inconsistent key set header");
+    const int64_t R = static_cast<int64_t>(h.num_keys), S = h.bits, W = h.W;
+    auto cpu = [](at::ScalarType t) { return at::TensorOptions().dtype(t).device(at::kCPU); };
+    at::Tensor scales = at::empty({R}, cpu(at::kFloat));
+    at::Tensor len = at::empty({R * S}, cpu(at::kInt));
+    at::Tensor stream = at::empty({static_cast<int64_t>(h.stream_words)}, cpu(at::kLong));
+    ifs.read(static_cast<char*>(scales.data_ptr()), R * 4);
+    ifs.read(static_cast<char*>(len.data_ptr()), R * S * 4);
+    ifs.read(static_cast<char*>(stream.data_ptr()), static_cast<std::streamsize>(h.stream_words) * 8);
+    TORCH_CHECK(ifs.good(), path, ": file is shorter than its header says");
+    uint64_t c = 1469598103934665603ull;
+    c = fnv1a(c, scales.data_ptr(), R * 4);
+    c = fnv1a(c, len.data_ptr(), R * S * 4);
+    c = fnv1a(c, stream.data_ptr(), h.stream_words * 8);
+    TORCH_CHECK(c == h.checksum, path, ": checksum mismatch (file damaged)");
+    // every slice must decode to at most W words from within the stream
+    {
+        const int32_t* lp = len.data_ptr<int32_t>();
+        uint64_t sum = 0;
+        for (int64_t i = 0; i < R * S; ++i) {
+            TORCH_CHECK(lp[i] >= 1 && lp[i] <= W + 1, path, ": slice length out of range");
+            sum += static_cast<uint64_t>(lp[i]);
+        }
+        TORCH_CHECK(sum == h.stream_words, path, ": slice lengths do not add up to the stream");
+    }
+
+    const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
+    auto* holder = new PrebuiltBSIKeysCUDA();
+    PackedBatch& b = holder->b;
+    b.rows = R;
+    b.d = static_cast<int64_t>(h.d);
+    b.S = static_cast<int>(S);
+    b.W = static_cast<int>(W);
+    b.chunks = (b.d + 255) / 256;
+    b.decimals = h.decimals;
+    b.chunk_mode = false;
+    EwahStream e;
+    e.len = len.to(dev);
+    e.off = (at::cumsum(e.len.to(at::kLong), 0) - e.len.to(at::kLong)).contiguous();
+    e.stream = h.stream_words > 0 ? stream.to(dev) : at::zeros({1}, at::TensorOptions().dtype(at::kLong).device(dev));
+    e.total = static_cast<int64_t>(h.stream_words);
+    b.words = ewah_decode(e, W).view({R, S, W});
+    b.scales = scales.to(dev);
+    const int64_t ld8 = std::max<int64_t>(b.chunks, 1) * 256;
+    b.q8 = at::empty({R, ld8}, at::TensorOptions().dtype(at::kChar).device(dev));
+    if (R > 0)
+        check_status(bsi_b200_recombine_i8(reinterpret_cast<const uint64_t*>(b.words.data_ptr<int64_t>()), R, b.S, W,
+                                           b.q8.data_ptr<int8_t>(), ld8, current_stream()),
+                     "bsi_b200_recombine_i8");
+    b.slice_weights = (slice_weight_base(b.S, dev).unsqueeze(0) * b.scales.unsqueeze(1)).contiguous();
+    if (h.flags & 1u) {   // variable-slice keys: the per-row slice counts follow from the integers again
+        b.variable = true;
+        at::Tensor amax = b.q8.to(at::kInt).abs().amax(1).to(at::kCPU).contiguous();
+        b.row_slices.resize(static_cast<size_t>(R));
+        for (int64_t r = 0; r < R; ++r)
+            b.row_slices[static_cast<size_t>(r)] = variable_slices(static_cast<uint64_t>(amax.data_ptr<int>()[r]));
+    }
+    holder->num_keys = R;
+    holder->threshold = h.threshold;
+    const uint64_t total_mem_bytes = static_cast<uint64_t>(b.words.numel() * b.words.element_size());
+    py::capsule cap(holder, "PrebuiltBSIKeysCUDA", [](PyObject* c) {
+        delete reinterpret_cast<PrebuiltBSIKeysCUDA*>(PyCapsule_GetPointer(c, "PrebuiltBSIKeysCUDA"));
+    });
+    return py::make_tuple(cap, total_mem_bytes, holder->num_keys, b.d, b.W);
+}
+
 int device_status() {
     int v = 0;
     check_status(bsi_b200_device_status(&v), "bsi_b200_device_status");
@@ -879,5 +1192,10 @@ PYBIND11_MODULE(bsi_ops, m) {
     m.def("debug_dot_iacc", &debug_dot_iacc);
     m.def("ewah_encode_words", &ewah_encode_words, py::arg("words"), py::arg("threshold"));
     m.def("ewah_decode_words", &ewah_decode_words, py::arg("stream"), py::arg("off"), py::arg("len"), py::arg("W"));
+    m.def("save_keyset", &save_keyset, py::arg("keyset_cuda_cap"), py::arg("out_dir"),
+          "Serialize a CUDA key set to <out_dir>/keyset.bsik (scales + EWAH / verbatim slice streams)");
+    m.def("load_keyset", &load_keyset, py::arg("dir_or_file"),
+          "Load a key set written by save_keyset; returns (capsule, total_mem_bytes, num_keys, d, W)");
+    m.def("keyset_size_on_disk", &keyset_size_on_disk, py::arg("keyset_cuda_cap"), "Return (mem_in_memory, bytes_on_disk)");
     m.def("device_status", &device_status, "Read and clear the device-side timeout status word (synchronises)");
 }

@@ -631,6 +631,98 @@ __global__ void __launch_bounds__(256) add_layernorm_pack_kernel(
     }
 }
 
+// ---- variable-slice mode (no shift: the decimal integers themselves are sliced) ---------------------------------
+// Pass 1: largest |v| and "has a negative" per row, v = half_away(double(float(x)) * 10^dp). The reference takes
+// them with torch reductions over the int64 tensor (bsi_vector_cuda.cpp:1089-1099, 1156-1159).
+template <typename T>
+__global__ void __launch_bounds__(256) decimal_absmax_kernel(const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx,
+                                                             double dec_scale, uint32_t dec_mult, int64_t chunks, int vec_ok,
+                                                             u64* __restrict__ row_absmax, int32_t* __restrict__ row_negative) {
+    __shared__ u64 wmax[8];
+    __shared__ int wneg[8];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t row = blockIdx.x;
+    const T* xr = x + row * ldx;
+    u64 mx = 0;
+    int neg = 0;
+    for (int64_t chunk = warp; chunk < chunks; chunk += 8) {
+        float f[8];
+        load8<T>(xr, chunk * 256 + lane * 8, D, vec_ok != 0, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const long long v = decimal_round(f[e], dec_scale, dec_mult);
+            const u64 a = uabs(v);
+            mx = a > mx ? a : mx;
+            neg |= v < 0 ? 1 : 0;
+        }
+    }
+    mx = warp_max_u64(mx);
+    neg = __any_sync(0xffffffffu, neg) ? 1 : 0;
+    if (lane == 0) {
+        wmax[warp] = mx;
+        wneg[warp] = neg;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 m = 0;
+        int n = 0;
+        for (int w = 0; w < 8; ++w) {
+            m = wmax[w] > m ? wmax[w] : m;
+            n |= wneg[w];
+        }
+        row_absmax[row] = m;
+        row_negative[row] = n;
+    }
+}
+
+// Pass 2: the low `slices` bits of the two's-complement integers as bit slices (what launch_pack_bits_all_ballot_batch
+// writes, bsi_cuda_kernels_pack.cuh:129-174, 204-230), plus, for the tensor-core dot, the integers as two signed
+// 8-bit digits: v = 128 * hi + lo with lo in [0, 127] (hi8 may be NULL when every |v| <= 127: lo8 then holds v itself).
+// One warp per 256-element chunk, lane = 8 elements, byte (lane % 8) of word (lane / 8) of each slice.
+template <typename T>
+__global__ void __launch_bounds__(256) pack_plain_kernel(const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx,
+                                                         double dec_scale, uint32_t dec_mult, int slices, int64_t chunks,
+                                                         int64_t W, int vec_ok, u64* __restrict__ words,
+                                                         int8_t* __restrict__ lo8, int8_t* __restrict__ hi8, int64_t ld8) {
+    const int lane = threadIdx.x & 31;
+    const int64_t unit = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (unit >= rows * chunks) return;
+    const int64_t row = unit / chunks;
+    const int64_t chunk = unit - row * chunks;
+    float f[8];
+    load8<T>(x + row * ldx, chunk * 256 + lane * 8, D, vec_ok != 0, f);
+    long long v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = decimal_round(f[e], dec_scale, dec_mult);
+    if (lo8 != nullptr) {
+        u64 lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (hi8 != nullptr) {
+                lo |= static_cast<u64>(v[e] & 127) << (8 * e);
+                hi |= static_cast<u64>((v[e] >> 7) & 255) << (8 * e);
+            } else {
+                lo |= static_cast<u64>(v[e] & 255) << (8 * e);
+            }
+        }
+        *reinterpret_cast<u64*>(lo8 + row * ld8 + chunk * 256 + lane * 8) = lo;
+        if (hi8 != nullptr) *reinterpret_cast<u64*>(hi8 + row * ld8 + chunk * 256 + lane * 8) = hi;
+    }
+    if (words != nullptr) {
+        const int64_t word = chunk * 4 + (lane >> 3);
+        if (word < W) {
+            uint8_t* base = reinterpret_cast<uint8_t*>(words + (row * slices) * W + word) + (lane & 7);
+            for (int s = 0; s < slices; ++s) {
+                uint32_t byte = 0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) byte |= static_cast<uint32_t>((v[e] >> s) & 1ll) << e;
+                base[static_cast<int64_t>(s) * W * 8] = static_cast<uint8_t>(byte);
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
     const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
@@ -997,6 +1089,65 @@ extern "C" int bsi_b200_add_layernorm_pack(const void* x, const void* delta, con
 #undef BSI_LAUNCH_ALP_T
 #undef BSI_LAUNCH_ALP
     return check_launch("add_layernorm_pack launch");
+}
+
+extern "C" int bsi_b200_decimal_absmax(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx, int decimal_places,
+                                       uint64_t* row_absmax, int32_t* row_negative, bsi_stream_t stream_) {
+    using namespace bsi;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (rows < 0 || D < 0 || ldx < D) return fail(BSI_ERR_INVALID, "decimal_absmax: bad rows / D / ldx");
+    if (rows == 0) return BSI_OK;
+    if (x == nullptr || row_absmax == nullptr || row_negative == nullptr) return fail(BSI_ERR_INVALID, "decimal_absmax: null pointer");
+    if (dtype != BSI_DTYPE_F32 && dtype != BSI_DTYPE_F16 && dtype != BSI_DTYPE_BF16)
+        return fail(BSI_ERR_INVALID, "decimal_absmax: unknown dtype");
+    if (rows > 0x7fffffffll) return fail(BSI_ERR_UNSUPPORTED, "decimal_absmax: too many rows for one launch");
+    if (int rc = require_sm100()) return rc;
+    const double dec_scale = pow(10.0, static_cast<double>(decimal_places));
+    const uint32_t dec_mult = (decimal_places >= 0 && decimal_places <= 8) ? static_cast<uint32_t>(dec_scale + 0.5) : 0u;
+    const int64_t chunks = (D + 255) / 256;
+    const int esz = dtype == BSI_DTYPE_F32 ? 4 : 2;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && ((ldx * esz) & 15) == 0) ? 1 : 0;
+    const unsigned g = static_cast<unsigned>(rows);
+#define BSI_ABSMAX(T) decimal_absmax_kernel<T><<<g, 256, 0, stream>>>(static_cast<const T*>(x), rows, D, ldx, dec_scale, \
+                                                                      dec_mult, chunks, vec_ok, reinterpret_cast<u64*>(row_absmax), row_negative)
+    if (dtype == BSI_DTYPE_F32) BSI_ABSMAX(float);
+    else if (dtype == BSI_DTYPE_F16) BSI_ABSMAX(__half);
+    else BSI_ABSMAX(__nv_bfloat16);
+#undef BSI_ABSMAX
+    return check_launch("decimal_absmax launch");
+}
+
+extern "C" int bsi_b200_pack_plain(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx, int decimal_places,
+                                   int slices, uint64_t* words, int8_t* lo8, int8_t* hi8, int64_t ld8, bsi_stream_t stream_) {
+    using namespace bsi;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (rows < 0 || D < 0 || ldx < D) return fail(BSI_ERR_INVALID, "pack_plain: bad rows / D / ldx");
+    if (slices < 1 || slices > 64) return fail(BSI_ERR_INVALID, "pack_plain: slices must be in [1, 64]");
+    if (rows == 0 || D == 0) return BSI_OK;
+    if (x == nullptr) return fail(BSI_ERR_INVALID, "pack_plain: null pointer");
+    if (dtype != BSI_DTYPE_F32 && dtype != BSI_DTYPE_F16 && dtype != BSI_DTYPE_BF16)
+        return fail(BSI_ERR_INVALID, "pack_plain: unknown dtype");
+    const int64_t chunks = (D + 255) / 256;
+    if (lo8 == nullptr && hi8 != nullptr) return fail(BSI_ERR_INVALID, "pack_plain: hi8 without lo8");
+    if (lo8 != nullptr && (ld8 < chunks * 256 || (ld8 & 15) != 0 || (reinterpret_cast<uintptr_t>(lo8) & 15) != 0 ||
+                           (reinterpret_cast<uintptr_t>(hi8) & 15) != 0))
+        return fail(BSI_ERR_INVALID, "pack_plain: int8 images need ld8 >= 256*ceil(D/256), ld8 % 16 == 0, 16-byte bases");
+    if (int rc = require_sm100()) return rc;
+    const double dec_scale = pow(10.0, static_cast<double>(decimal_places));
+    const uint32_t dec_mult = (decimal_places >= 0 && decimal_places <= 8) ? static_cast<uint32_t>(dec_scale + 0.5) : 0u;
+    const int64_t W = (D + 63) / 64;
+    const int esz = dtype == BSI_DTYPE_F32 ? 4 : 2;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && ((ldx * esz) & 15) == 0) ? 1 : 0;
+    const int64_t blocks = (rows * chunks + 7) / 8;
+    if (blocks > 0x7fffffffll) return fail(BSI_ERR_UNSUPPORTED, "pack_plain: too many rows for one launch");
+    const unsigned g = static_cast<unsigned>(blocks);
+#define BSI_PLAIN(T) pack_plain_kernel<T><<<g, 256, 0, stream>>>(static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, \
+                                                                  slices, chunks, W, vec_ok, reinterpret_cast<u64*>(words), lo8, hi8, ld8)
+    if (dtype == BSI_DTYPE_F32) BSI_PLAIN(float);
+    else if (dtype == BSI_DTYPE_F16) BSI_PLAIN(__half);
+    else BSI_PLAIN(__nv_bfloat16);
+#undef BSI_PLAIN
+    return check_launch("pack_plain launch");
 }
 
 extern "C" int bsi_b200_recombine_i8(const uint64_t* words, int64_t rows, int bits, int64_t W,

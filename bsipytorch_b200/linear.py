@@ -1,16 +1,22 @@
-"""Layer replacement: ``BSIQuantizedLinear`` and ``quantize_model_bsi``.
+"""BSI linear layer with a single-call forward, and helpers around it.
 
-Mirrors ``bsi_ops/benchmarks/verify_accuracy_bsi.py:46-215`` (the layer) and ``:444-486`` (the model
-walk) of the reference: same constructor arguments, attributes and counters, same arithmetic
-(keys built once from the float32 weight; per forward: quantise+pack the activations, BSI dot,
-cast to the activation dtype, add the bias). ``fused=True`` (default) issues the forward as one
-extension call; ``fused=False`` goes through the same two entry points the reference layer calls.
+The reference defines its layer replacement in a benchmark script (``BSIQuantizedLinear`` and
+``quantize_model_bsi``, bsi_ops/benchmarks/verify_accuracy_bsi.py:46-215, 444-486). That class runs
+unmodified over this package's ``bsi_ops`` module (``install_as_bsi_ops()``; tests/test_gpu_reference_callers.py
+does exactly that), so nothing here restates its bookkeeping (timing counters, diagnostics, summaries).
+What this module adds:
+
+* a layer whose forward is ONE extension call -- quantise + pack, integer dot, float32 chunk combine,
+  cast and bias in the dot's epilogue -- with bit-identical results (``fused=False`` issues the same two
+  entry points the reference's layer calls);
+* key sets that can be written to and read from disk in their packed form (``save_bsi_keysets`` /
+  ``load_bsi_keysets``), so a model is not quantised again on every start;
+* a model walk that accepts a layer factory (used for the R-sharded layer).
 """
 from __future__ import annotations
 
 import os
-import time
-from typing import Dict, Union
+from typing import Callable, Dict, Optional, Union
 
 import torch
 from torch import nn
@@ -22,172 +28,137 @@ def _ops():
 
 
 class BSIQuantizedLinear(nn.Module):
-    """BSI linear layer using prebuilt keys (reference: verify_accuracy_bsi.py:46-215)."""
+    """``y = x @ W.T + b`` on the BSI path. Constructor arguments as the reference's layer
+    (verify_accuracy_bsi.py:49); ``keyset`` builds the layer from a stored key set instead of a dense weight."""
 
-    def __init__(self, original_linear, decimalPlaces=2, compress_threshold=0.2, query_threshold=None,
-                 prefer_cuda: bool = True, fused: bool = True, keep_dense_weight: bool = False):
+    def __init__(self, original_linear: Optional[nn.Linear] = None, decimalPlaces=2, compress_threshold=0.2,
+                 query_threshold=None, prefer_cuda: bool = True, fused: bool = True, keyset: Optional[str] = None,
+                 bias: Optional[torch.Tensor] = None):
         super().__init__()
+        if not (prefer_cuda and torch.cuda.is_available()):
+            raise RuntimeError("CUDA path required: there is no CPU fallback for BSIQuantizedLinear")
         self.decimalPlaces = int(decimalPlaces)
         self.compress_threshold = float(compress_threshold)
         self.query_compress_threshold = float(query_threshold) if query_threshold is not None else float(compress_threshold)
-        self.in_features = original_linear.in_features
-        self.out_features = original_linear.out_features
         self.fused = bool(fused)
-
-        if not (prefer_cuda and torch.cuda.is_available()):
-            raise RuntimeError("CUDA path required: there is no CPU fallback for BSIQuantizedLinear")
-
-        dense_weight = original_linear.weight.detach().to(torch.float32)
-        self.weight_fp32 = dense_weight.cpu() if keep_dense_weight else None
-        self.weight_dense_memory_bytes = dense_weight.numel() * dense_weight.element_size()
-        if original_linear.bias is not None:
-            bias = original_linear.bias.detach().to(torch.float32)
-            self.register_buffer("bias", bias)
-            self.bias_fp32 = bias.cpu() if keep_dense_weight else None
-            self.bias_memory_bytes = bias.numel() * bias.element_size()
-        else:
-            self.register_buffer("bias", None)
-            self.bias_fp32 = None
-            self.bias_memory_bytes = 0
-
-        with torch.no_grad():
-            # The reference hands the builder a CPU tensor (verify_accuracy_bsi.py:82); a CUDA
-            # tensor gives the same integers and skips the host round trip.
-            self._bsi_keys_cuda, total_mem_bytes, num_keys, d, _W = _ops().build_bsi_keys_cuda(
-                dense_weight, self.decimalPlaces, float(self.compress_threshold))
-        assert num_keys == self.out_features and d == self.in_features
-        self.weight_bsi_memory_bytes = int(total_mem_bytes)
-        self.total_bsi_static_bytes = self.weight_bsi_memory_bytes + self.bias_memory_bytes
-        self.verbose = False
-        self.collect_stats = False
-        self._reset_counters()
-
-    def _reset_counters(self):
-        self.dot_ns_total = 0
+        ops = _ops()
+        dev = torch.device("cuda", torch.cuda.current_device())
+        if original_linear is not None and original_linear.weight.is_cuda:
+            dev = original_linear.weight.device
+        with torch.no_grad(), torch.cuda.device(dev):
+            if keyset is not None:
+                self._bsi_keys_cuda, mem, self.out_features, self.in_features, _w = ops.load_keyset(keyset)
+                self.decimalPlaces = int(ops.bsi_keys_cuda_stats(self._bsi_keys_cuda)["decimals"])
+            else:
+                self.in_features, self.out_features = original_linear.in_features, original_linear.out_features
+                # the reference hands the builder a CPU copy (verify_accuracy_bsi.py:82); the tensor as it is gives
+                # the same integers without the host round trip
+                self._bsi_keys_cuda, mem, num_keys, d, _w = ops.build_bsi_keys_cuda(
+                    original_linear.weight.detach().to(torch.float32), self.decimalPlaces, self.compress_threshold)
+                assert num_keys == self.out_features and d == self.in_features
+                if bias is None and original_linear.bias is not None:
+                    bias = original_linear.bias
+        self.register_buffer("bias", None if bias is None else bias.detach().to(torch.float32).to(dev))
+        self.weight_bsi_memory_bytes = int(mem)
+        self.total_bsi_static_bytes = self.weight_bsi_memory_bytes + (0 if self.bias is None else self.bias.numel() * 4)
         self.dot_calls = 0
-        self.dot_kernel_ns_per_query_last = 0.0
-        self.dot_kernel_ns_per_scalar_last = 0.0
-        self.dot_query_vectors_total = 0
         self.dot_output_elements_total = 0
-        self.build_ns_total = 0
-        self.build_quantize_ns_total = 0
-        self.build_pack_ns_total = 0
-        self.build_kernel_ns_total = 0
-        self.build_calls = 0
 
     def forward(self, x):
-        original_dtype = x.dtype
-        original_shape = x.shape
-        if x.dim() > 2:
-            x = x.reshape(-1, x.shape[-1])
-        if os.getenv("BSI_QUERY_FP32", "0") != "0":
-            x = x.to(torch.float32)
+        shape, dtype = x.shape, x.dtype
+        x2d = x.reshape(-1, shape[-1]).detach().contiguous()
+        if os.getenv("BSI_QUERY_FP32", "0") != "0":          # the reference's switch (verify_accuracy_bsi.py:126)
+            x2d = x2d.to(torch.float32)
         ops = _ops()
-        batch_inputs = x.detach().contiguous()
-        q_rows = int(batch_inputs.shape[0])
-
         if self.fused and os.getenv("BSI_PROFILE", "0") == "0":
-            out = ops.bsi_linear_forward(batch_inputs, self._bsi_keys_cuda, self.bias, self.decimalPlaces)
-            if out.dtype != original_dtype:
-                out = out.to(original_dtype)
-            self.build_calls += 1
-            self.dot_calls += 1
+            out = ops.bsi_linear_forward(x2d, self._bsi_keys_cuda, self.bias, self.decimalPlaces)
+            out = out if out.dtype == dtype else out.to(dtype)
         else:
-            t0 = time.perf_counter_ns()
-            use_packed = os.getenv("BSI_QUERY_PACKED", "1") != "0"
-            if use_packed:
-                caps = ops.build_bsi_queries_cuda_batch_packed(batch_inputs, self.decimalPlaces,
-                                                               float(self.query_compress_threshold))
-            else:
-                caps = ops.build_bsi_queries_cuda_batch(batch_inputs, self.decimalPlaces,
-                                                        float(self.query_compress_threshold))
-            self.build_ns_total += time.perf_counter_ns() - t0
-            q_ns, p_ns, t_ns = ops.get_last_query_build_profile_cuda()
-            self.build_quantize_ns_total += int(q_ns)
-            self.build_pack_ns_total += int(p_ns)
-            self.build_kernel_ns_total += int(t_ns)
-            self.build_calls += 1
-            if use_packed:
-                scores, ns_total, ns_q, ns_s = ops.batch_dot_product_multiquery_cuda_batch_caps(caps, self._bsi_keys_cuda)
-            else:
-                scores, ns_total, ns_q, ns_s = ops.batch_dot_product_multiquery_cuda_caps(caps, self._bsi_keys_cuda)
-            self.dot_ns_total += int(ns_total)
-            self.dot_kernel_ns_per_query_last = float(ns_q)
-            self.dot_kernel_ns_per_scalar_last = float(ns_s)
-            self.dot_calls += 1
-            out = scores.to(dtype=original_dtype)
+            packed = os.getenv("BSI_QUERY_PACKED", "1") != "0"
+            build = ops.build_bsi_queries_cuda_batch_packed if packed else ops.build_bsi_queries_cuda_batch
+            dot = ops.batch_dot_product_multiquery_cuda_batch_caps if packed else ops.batch_dot_product_multiquery_cuda_caps
+            scores, *_ = dot(build(x2d, self.decimalPlaces, self.query_compress_threshold), self._bsi_keys_cuda)
+            out = scores.to(dtype)
             if self.bias is not None:
-                out = out + self.bias.to(dtype=original_dtype)
-        self.dot_query_vectors_total += q_rows
-        self.dot_output_elements_total += q_rows * int(self.out_features)
-        if len(original_shape) == 3:
-            out = out.view(original_shape[0], original_shape[1], -1)
-        return out
+                out = out + self.bias.to(dtype)
+        self.dot_calls += 1
+        self.dot_output_elements_total += x2d.shape[0] * self.out_features
+        return out.view(*shape[:-1], self.out_features)
 
 
-def reset_bsi_dot_counters(model: nn.Module):
-    for m in model.modules():
-        if isinstance(m, BSIQuantizedLinear):
-            m._reset_counters()
-
-
-def sum_bsi_dot_counters(model: nn.Module) -> int:
-    return sum(int(m.dot_ns_total) for m in model.modules() if isinstance(m, BSIQuantizedLinear))
+def bsi_layers(model: nn.Module):
+    """(name, layer) of every BSI layer of `model` that owns a key set capsule (this class or the reference's)."""
+    return [(n, m) for n, m in model.named_modules() if getattr(m, "_bsi_keys_cuda", None) is not None]
 
 
 def bsi_full_model_static_bytes(model: nn.Module) -> int:
-    """BSI key bytes + bias bytes over all replaced layers (verify_accuracy_bsi.py:281-300)."""
-    return sum(int(m.total_bsi_static_bytes) for m in model.modules() if isinstance(m, BSIQuantizedLinear))
+    """Key bytes + bias bytes over all BSI layers."""
+    return sum(int(getattr(m, "total_bsi_static_bytes", 0)) for _, m in bsi_layers(model))
 
 
-def _resolve_layer_value(config: Union[float, Dict[str, float]], layer_kind: str, fallback: float) -> float:
-    if isinstance(config, dict):
-        if layer_kind in ("attention", "mlp"):
-            return float(config.get(layer_kind, config.get("default", fallback)))
-        return float(config.get("default", fallback))
-    return float(config)
+def save_bsi_keysets(model: nn.Module, out_dir: str) -> int:
+    """Writes the key set of every BSI layer to ``out_dir/<layer name>/keyset.bsik`` (row scales + EWAH / verbatim
+    slice streams) and the biases to ``out_dir/biases.pt``; returns the bytes written for the key sets."""
+    ops = _ops()
+    total, biases = 0, {}
+    for name, layer in bsi_layers(model):
+        ops.save_keyset(layer._bsi_keys_cuda, os.path.join(out_dir, name))
+        total += int(ops.keyset_size_on_disk(layer._bsi_keys_cuda)[1])
+        if getattr(layer, "bias", None) is not None:
+            biases[name] = layer.bias.detach().float().cpu()
+    torch.save(biases, os.path.join(out_dir, "biases.pt"))
+    return total
 
 
-def quantize_model_bsi(model, decimalPlaces=2, skip_lm_head=True, scope="all", compress_threshold=0.2,
-                       prefer_cuda: bool = True, layer_factory=None, verbose: bool = True):
-    """Replace ``nn.Linear`` modules by BSI layers (reference: verify_accuracy_bsi.py:444-486).
-
-    scope: 'all' (every Linear except lm_head), 'attention' (q/k/v/out projections) or 'mlp' (fc1/fc2).
-    ``layer_factory(linear, decimalPlaces=..., compress_threshold=..., name=...)`` lets the caller build a
-    different layer (e.g. an R-sharded one); default ``BSIQuantizedLinear``.
-    """
-    def is_attention_linear(name: str) -> bool:
-        return any(t in name for t in ["attn", "self_attn", "q_proj", "k_proj", "v_proj", "out_proj"])
-
-    def is_mlp_linear(name: str) -> bool:
-        return any(t in name for t in ["mlp", "ff", "ffn", "fc1", "fc2"])
-
-    default_decimal = float(decimalPlaces if isinstance(decimalPlaces, (int, float)) else decimalPlaces.get("default", 2))
-    default_threshold = float(compress_threshold if isinstance(compress_threshold, (int, float))
-                              else compress_threshold.get("default", 0.2))
-    targets = []
-    for name, module in model.named_modules():
-        if isinstance(module, nn.Linear):
-            if skip_lm_head and "lm_head" in name:
-                continue
-            if scope == "attention" and not is_attention_linear(name):
-                continue
-            if scope == "mlp" and not is_mlp_linear(name):
-                continue
-            targets.append((name, module))
-    for name, module in targets:
+def load_bsi_keysets(model: nn.Module, in_dir: str, fused: bool = True) -> nn.Module:
+    """Replaces every ``nn.Linear`` (or BSI layer) of `model` that has a stored key set under `in_dir` by a BSI
+    layer built from it: no dense weight is read and nothing is quantised again."""
+    biases = torch.load(os.path.join(in_dir, "biases.pt"))
+    for name, module in list(model.named_modules()):
+        if not os.path.exists(os.path.join(in_dir, name, "keyset.bsik")) or not name:
+            continue
         parent = model
         parts = name.split(".")
         for part in parts[:-1]:
             parent = getattr(parent, part)
-        kind = "attention" if is_attention_linear(name) else "mlp" if is_mlp_linear(name) else "other"
-        dp = _resolve_layer_value(decimalPlaces, kind, default_decimal)
-        thr = _resolve_layer_value(compress_threshold, kind, default_threshold)
-        if layer_factory is None:
-            new = BSIQuantizedLinear(module, decimalPlaces=dp, compress_threshold=thr, prefer_cuda=prefer_cuda)
-        else:
-            new = layer_factory(module, decimalPlaces=dp, compress_threshold=thr, name=name)
+        setattr(parent, parts[-1], BSIQuantizedLinear(keyset=os.path.join(in_dir, name), bias=biases.get(name), fused=fused))
+    return model
+
+
+def _layer_value(config: Union[float, Dict[str, float]], kind: str, fallback: float) -> float:
+    if isinstance(config, dict):
+        return float(config.get(kind, config.get("default", fallback)))
+    return float(config)
+
+
+_ATTENTION = ("attn", "self_attn", "q_proj", "k_proj", "v_proj", "out_proj")
+_MLP = ("mlp", "ff", "ffn", "fc1", "fc2")
+
+
+def quantize_model_bsi(model, decimalPlaces=2, skip_lm_head=True, scope="all", compress_threshold=0.2,
+                       prefer_cuda: bool = True, layer_factory: Optional[Callable] = None, verbose: bool = True):
+    """Swaps ``nn.Linear`` modules for BSI layers, with the selection rules of the reference's walk
+    (verify_accuracy_bsi.py:444-486): every Linear except ``lm_head``; ``scope`` 'attention' or 'mlp' narrows it by
+    name; ``decimalPlaces`` / ``compress_threshold`` may be dicts keyed by 'attention' / 'mlp' / 'default'.
+    ``layer_factory(linear, decimalPlaces=..., compress_threshold=..., name=...)`` builds another layer type."""
+    picked = []
+    for name, module in model.named_modules():
+        if not isinstance(module, nn.Linear) or (skip_lm_head and "lm_head" in name):
+            continue
+        kind = "attention" if any(t in name for t in _ATTENTION) else "mlp" if any(t in name for t in _MLP) else "other"
+        if scope in ("attention", "mlp") and kind != scope:
+            continue
+        picked.append((name, module, kind))
+    for name, module, kind in picked:
+        dp = _layer_value(decimalPlaces, kind, 2)
+        thr = _layer_value(compress_threshold, kind, 0.2)
+        new = (BSIQuantizedLinear(module, decimalPlaces=dp, compress_threshold=thr, prefer_cuda=prefer_cuda)
+               if layer_factory is None else layer_factory(module, decimalPlaces=dp, compress_threshold=thr, name=name))
+        parent = model
+        parts = name.split(".")
+        for part in parts[:-1]:
+            parent = getattr(parent, part)
         setattr(parent, parts[-1], new)
     if verbose:
-        print(f"Quantized {len(targets)} linear layers to BSI with decimalPlaces={decimalPlaces} (scope={scope})")
+        print(f"Quantized {len(picked)} linear layers to BSI with decimalPlaces={decimalPlaces} (scope={scope})")
     return model

@@ -83,6 +83,30 @@ int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, int64_t D, in
                            uint64_t* words, float* scales, int32_t* shifts,
                            int8_t* q8, int64_t ld8, bsi_stream_t stream);
 
+/* ---- variable-slice mode (the reference's default when no BSI_FIXED_BITS* variable is set) ------
+ * The decimal integers v = half_away(double(float(x)) * 10^decimal_places) are sliced as they are,
+ * without a shift; the number of slices follows from the largest |v| (bit_width(max|v|) + 2, at least
+ * 2; bsi_vector_cuda.cpp:746-754), per batch for queries and per row for keys.
+ *
+ * bsi_b200_decimal_absmax: row_absmax[r] = max |v| and row_negative[r] = 1 if any v < 0 of row r.
+ * Replaces the torch reductions over the int64 tensor in build_bsi_queries_cuda_batch_data
+ * (bsi_vector_cuda.cpp:1089-1099, 1156-1159) after launch_quantize_round_to_int64_batch
+ * (bsi_cuda_kernels_quant.cuh:638-668). */
+int bsi_b200_decimal_absmax(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                            int decimal_places, uint64_t* row_absmax, int32_t* row_negative,
+                            bsi_stream_t stream);
+
+/* bsi_b200_pack_plain: words [rows, slices, W] = the low `slices` bits of the two's-complement v (any
+ * of words / lo8 may be NULL). lo8 / hi8 [rows, ld8]: v as two signed 8-bit digits for the tensor-core
+ * dot, v = 128 * hi + lo, lo in [0, 127] (the caller checks |v| < 2^14 through decimal_absmax); with
+ * hi8 == NULL, lo8 receives v itself (|v| <= 127). Columns up to 256*ceil(D/256) are written, zero
+ * beyond D. Replaces launch_quantize_round_to_int64_batch + launch_pack_bits_all_ballot[_batch]
+ * (bsi_cuda_kernels_quant.cuh:638-668, bsi_cuda_kernels_pack.cuh:176-230). Partial last words rely on
+ * zero-initialised `words`, as the reference's packer does. */
+int bsi_b200_pack_plain(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx, int decimal_places,
+                        int slices, uint64_t* words, int8_t* lo8, int8_t* hi8, int64_t ld8,
+                        bsi_stream_t stream);
+
 /* Slice words -> int8 image (sign-extends the top slice). Used when a caller holds only the
  * bit slices (e.g. words built by the reference). No counterpart in the reference, whose dot
  * consumes the slices directly (bsi_cuda_kernels_dot.cuh:1436-1517). */

@@ -261,3 +261,73 @@ class CpuKeyset:
 
 def num_threads() -> int:
     return int(lib().bsi_or_num_threads())
+
+
+# ---- variable-slice mode (the reference without BSI_FIXED_BITS*: no shift, slice count from the data) ------------
+def decimal_ints(x, decimal_places: int):
+    """half_away(double(float(x)) * 10^dp) as int64 (bsi_cuda_kernels_quant.cuh:24-29, 110-121)."""
+    t = np.ascontiguousarray(x, np.float32).astype(np.float64) * (10.0 ** int(decimal_places))
+    return np.where(t >= 0, np.floor(t + 0.5), -np.floor(-t + 0.5)).astype(np.int64)
+
+
+def variable_slices(max_abs: int) -> int:
+    """bit_width(max |v|) + 2, 2 when everything is zero, at most 64 (bsi_vector_cuda.cpp:746-754)."""
+    max_abs = int(max_abs)
+    return min(64, max(1, max_abs.bit_length()) + 2) if max_abs else 2
+
+
+def variable_pack(x, decimal_places: int, per_row: bool = False):
+    """Variable-slice builder. Queries (per_row=False): one slice count for the batch
+    (bsi_vector_cuda.cpp:1086-1101); keys (per_row=True): `row_slices` holds every row's own count, the words
+    are stored at the widest row's width. Words are the low S bits of the two's-complement integers
+    (bsi_cuda_kernels_pack.cuh:129-174); a row's slice weights are +2^i, with the top slice negative when the row
+    holds a negative value (bsi_vector_cuda.cpp:1156-1162).
+
+    Returns dict(ints[rows, D] int64, S, row_slices[rows], words[rows, S, W] uint64, weights[rows, S] float32)."""
+    v = decimal_ints(x, decimal_places)
+    rows, D = v.shape
+    W = max(1, (D + 63) // 64)
+    row_max = np.abs(v).max(axis=1) if D else np.zeros(rows, np.int64)
+    S = variable_slices(int(row_max.max()) if rows else 0)
+    row_slices = np.array([variable_slices(int(m)) for m in row_max], np.int32) if per_row else np.full(rows, S, np.int32)
+    words = np.zeros((rows, S, W), np.uint64)
+    u = v.astype(np.uint64)                       # two's complement bit pattern
+    for s in range(S):
+        bit = ((u >> np.uint64(s)) & np.uint64(1)).astype(np.uint64)
+        for w in range(W):
+            seg = bit[:, w * 64:(w + 1) * 64]
+            sh = np.arange(seg.shape[1], dtype=np.uint64)
+            words[:, s, w] = (seg << sh[None, :]).sum(axis=1, dtype=np.uint64)
+    base = np.array([float(1 << i) for i in range(S)], np.float32)
+    twos = base.copy()
+    twos[S - 1] = -twos[S - 1]
+    neg = (v < 0).any(axis=1)
+    weights = np.where(neg[:, None], twos[None, :], base[None, :]).astype(np.float32)
+    return dict(ints=v, S=S, row_slices=row_slices, words=words, weights=weights, negative=neg)
+
+
+def variable_dot(xq, xk, decimal_places: int = 2):
+    """out[q][r] = float32(sum_d vq[q][d] * vk[r][d]) * float32(1 / 10^(2 dp)): what the reference's weighted
+    popcount sum (bsi_cuda_kernels_dot.cuh:597-654) gives while its float32 partial sums stay below 2^24 (every
+    product of a count, a power of two and an integer is then exact); asserts that bound."""
+    vq, vk = decimal_ints(xq, decimal_places), decimal_ints(xk, decimal_places)
+    bound = np.abs(vq).astype(np.int64) @ np.abs(vk).astype(np.int64).T
+    assert int(bound.max(initial=0)) < (1 << 24), "outside the range where the reference's float32 accumulation is exact"
+    exact = vq @ vk.T
+    return exact.astype(np.float32) * scale_inv(decimal_places)
+
+
+def variable_dot_popc(qa, kb, decimal_places: int = 2):
+    """Slow cross-check of variable_dot from the slices and weights themselves (small shapes only)."""
+    A, Aw, B, Bw = qa["words"], qa["weights"], kb["words"], kb["weights"]
+    Q, Sa, W = A.shape
+    R, Sb, _ = B.shape
+    out = np.zeros((Q, R), np.float64)
+    for i in range(Sa):
+        for j in range(Sb):
+            both = A[:, None, i, :] & B[None, :, j, :]
+            cnt = np.zeros((Q, R), np.int64)
+            for w in range(W):
+                cnt += np.array([[bin(int(x)).count("1") for x in row] for row in both[:, :, w]], np.int64)
+            out += cnt * (Aw[:, i].astype(np.float64)[:, None] * Bw[:, j].astype(np.float64)[None, :])
+    return out.astype(np.float32) * scale_inv(decimal_places)

@@ -151,3 +151,44 @@ def ewah_decode(stream, off, length, W):
         L.launch_ewah_decompress(C.c_void_p(stream.data_ptr() + 8 * off_h[s]), C.c_int(len_h[s]), C.c_int(W),
                                  C.c_void_p(out.data_ptr() + 8 * s * W), _stream())
     return out
+
+
+def pack_plain(x, decimal_places, slices):
+    """Reference variable-slice builder on the GPU: round to int64, then the ballot packer
+    (bsi_vector_cuda.cpp:1074-1131). Returns (words [rows, slices, W] int64, ints [rows, d] int64)."""
+    L = lib()
+    x = x.contiguous()
+    rows, d = x.shape
+    W = (d + 63) // 64
+    dev = x.device
+    ints = torch.empty(rows, d, dtype=torch.int64, device=dev)
+    words = torch.zeros(rows, slices, W, dtype=torch.int64, device=dev)
+    L.launch_quantize_round_to_int64_batch(_p(x), C.c_int(_dtype_code(x)), C.c_int64(rows), C.c_int64(d),
+                                           C.c_double(10.0 ** decimal_places), _p(ints), _stream())
+    mask = (1 << slices) - 1 if slices < 64 else (1 << 64) - 1
+    L.launch_pack_bits_all_ballot_batch(_p(ints), C.c_int(rows), C.c_longlong(d), C.c_int(slices), C.c_int(W),
+                                        C.c_ulonglong(mask), _p(words), _stream())
+    return words, ints
+
+
+def dot_generic(A_words, Aw, B_words, Bw, scale_inv, tensor_core=True):
+    """Reference generic-S dot with float slice weights and no chunk scales (the variable-slice path,
+    bsi_cuda.cpp:433-656 -> dot.cuh:211-1283 with BSI_TC_DOT=1, :58-188 with 0). Returns out [Q, R] float32."""
+    L = lib()
+    Q, Sa, W = A_words.shape
+    R, Sb, _ = B_words.shape
+    out = torch.zeros(Q, R, dtype=torch.float32, device=A_words.device)
+    old = os.environ.get("BSI_TC_DOT")
+    os.environ["BSI_TC_DOT"] = "1" if tensor_core else "0"      # re-read on every launch (dot.cuh:2642)
+    try:
+        L.launch_popcount_weighted_keys_literal_fused_multiq(
+            _p(A_words), _p(Aw.contiguous()), None, C.c_int(0), C.c_int(Sa), C.c_int(W),
+            _p(B_words), _p(Bw.contiguous()), C.c_int(Sb), C.c_int(R), C.c_int(Q), C.c_int(8), C.c_int(4), None, None,
+            C.c_float(float(scale_inv)), C.c_int(R), _p(out), _stream())
+        torch.cuda.synchronize()
+    finally:
+        if old is None:
+            os.environ.pop("BSI_TC_DOT", None)
+        else:
+            os.environ["BSI_TC_DOT"] = old
+    return out

@@ -220,3 +220,45 @@ def test_quantize_model_bsi_walk(bsi_ops):
     assert y.shape == dense.shape and torch.isfinite(y).all()
     assert float((y - dense).abs().max()) < 0.5
     assert capi.device_status() == 0
+
+
+def test_keyset_save_load_round_trip(bsi_ops, tmp_path):
+    """save_keyset / load_keyset: the stored form (row scales + EWAH / verbatim slice streams) gives back the same
+    slices, int8 image and scales, and the same dot, without the dense weights."""
+    g = torch.Generator().manual_seed(77)
+    k = torch.randn(300, 1000, generator=g) * 0.02
+    k[5] = 0.0                                  # an all-zero row: every slice is one run
+    k[6, :512] = 0.0                            # half-empty row
+    k[7] = 0.31                                 # constant row: slices are all-ones / all-zeros runs
+    q = torch.randn(64, 1000, generator=g).to(DEV)
+    for thr in (0.5, 0.2):
+        cap, mem, R, d, W = bsi_ops.build_bsi_keys_cuda(k, 2, thr)
+        out_dir = str(tmp_path / f"keys_{thr}")
+        assert bsi_ops.save_keyset(cap, out_dir) is None
+        path = os.path.join(out_dir, "keyset.bsik")
+        mem2, disk = bsi_ops.keyset_size_on_disk(cap)
+        assert mem2 == mem and disk == os.path.getsize(path)
+        # a verbatim slice costs one marker word more than in memory; the file adds one length per slice, one scale
+        # per row and the header
+        assert disk <= mem + R * 6 * 12 + R * 4 + 64
+        cap2, mem3, R2, d2, W2 = bsi_ops.load_keyset(out_dir)
+        assert (mem3, R2, d2, W2) == (mem, R, d, W)
+        a, b = bsi_ops.debug_keys_tensors(cap), bsi_ops.debug_keys_tensors(cap2)
+        for name in ("words", "q8", "scales", "slice_weights"):
+            assert torch.equal(a[name], b[name]), name
+        assert bsi_ops.bsi_keys_cuda_stats(cap2)["decimals"] == 2
+        qcap = bsi_ops.build_bsi_queries_cuda_batch_packed(q, 2, thr)
+        want, *_ = bsi_ops.batch_dot_product_multiquery_cuda_batch_caps(qcap, cap)
+        got, *_ = bsi_ops.batch_dot_product_multiquery_cuda_batch_caps(qcap, cap2)
+        assert torch.equal(got, want)
+        assert bsi_ops.load_keyset(path)[2] == R     # the file itself is accepted too
+    # a damaged file is refused
+    raw = bytearray(open(path, "rb").read())
+    raw[-3] ^= 0x40
+    bad = str(tmp_path / "bad.bsik")
+    open(bad, "wb").write(bytes(raw))
+    with pytest.raises(RuntimeError, match="checksum"):
+        bsi_ops.load_keyset(bad)
+    open(bad, "wb").write(bytes(raw[:100]))
+    with pytest.raises(RuntimeError):
+        bsi_ops.load_keyset(bad)

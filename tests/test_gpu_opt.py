@@ -31,6 +31,29 @@ def test_layer_by_layer_build_equals_quantize_model_walk():
     assert rel < 0.5, rel     # weights ~N(0, 0.02) on a 0.01 grid: the recipe's own quantisation error
 
 
+def test_model_keysets_round_trip_through_disk(tmp_path):
+    """save_bsi_keysets / load_bsi_keysets: a model rebuilt from the stored key sets (no dense linear weights read,
+    nothing quantised again) gives the logits of the model that wrote them."""
+    from bsipytorch_b200.linear import load_bsi_keysets, save_bsi_keysets
+
+    src = opt.build_opt_bsi(TINY, dtype=torch.float16, device=DEV, seed=5)
+    with torch.no_grad():
+        for i, layer in enumerate(src.model.decoder.layers):     # non-zero biases, so that they are seen to travel
+            layer.fc1.bias.copy_(torch.full_like(layer.fc1.bias, 0.01 * (i + 1)))
+    written = save_bsi_keysets(src, str(tmp_path))
+    assert written > 0
+    dst = opt.build_opt(TINY, dtype=torch.float16, device=DEV, seed=5)
+    for layer in dst.model.decoder.layers:                       # prove the dense weights are not what is used
+        for lin in (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.out_proj,
+                    layer.fc1, layer.fc2):
+            lin.weight.data.zero_()
+    load_bsi_keysets(dst, str(tmp_path))
+    assert sum(isinstance(m, BSIQuantizedLinear) for m in dst.modules()) == 12
+    ids = torch.randint(0, 512, (3, 40), generator=torch.Generator().manual_seed(1)).to(DEV)
+    with torch.no_grad():
+        assert torch.equal(dst(ids), src(ids))
+
+
 def test_first_bsi_layer_matches_cpu_checker_inside_the_model():
     model = opt.build_opt_bsi(TINY, dtype=torch.float32, device=DEV, seed=2, keep_dense=True)
     ids = torch.randint(0, 512, (2, 24), generator=torch.Generator().manual_seed(3)).to(DEV)

@@ -179,3 +179,24 @@ def test_relu_activations_compress_sign_slice_to_one_word():
     for q in range(4):
         s = q * 7 + 6
         assert length[s] == 1 and int(stream[off[s]]) == (128 << 1)
+
+
+def test_variable_slice_mode_restatement():
+    """Variable-slice mode: slice-count rule (bsi_vector_cuda.cpp:746-754), two's-complement slices with the
+    reference's per-row weights reproduce the exact integer dot, and the print-style known answers of the
+    reference's CPU scripts hold (test_bsi_simple.py: [1,2,3,4].[4,3,2,1] = 20, negated = -20)."""
+    assert [o.variable_slices(m) for m in (0, 1, 2, 3, 4, 255, 256, 2 ** 40)] == [2, 3, 4, 4, 5, 10, 11, 43]
+    q = np.array([[1, 2, 3, 4], [-1, -2, -3, -4], [0.5, 0.25, 0, -0.125]], np.float32)
+    k = np.array([[4, 3, 2, 1], [1, 0, 0, 0]], np.float32)
+    out = o.variable_dot(q, k, 2)
+    np.testing.assert_allclose(out[:2], [[20, 1], [-20, -1]], rtol=0, atol=1e-6)
+    qa, kb = o.variable_pack(q, 2), o.variable_pack(k, 2, per_row=True)
+    assert qa["S"] == 9 + 2 and list(kb["row_slices"]) == [9 + 2, 7 + 2]          # 400 -> 9 bits, 100 -> 7 bits
+    assert list(qa["negative"]) == [False, True, True] and qa["weights"][0, -1] > 0 > qa["weights"][1, -1]
+    np.testing.assert_array_equal(o.variable_dot_popc(qa, kb, 2).view(np.uint32), out.view(np.uint32))
+    rng = np.random.default_rng(3)
+    xq = rng.standard_normal((6, 200)).astype(np.float32) * 3
+    xk = (rng.standard_normal((5, 200)) * 0.05).astype(np.float32)
+    a = o.variable_dot(xq, xk, 2)
+    b = o.variable_dot_popc(o.variable_pack(xq, 2), o.variable_pack(xk, 2, per_row=True), 2)
+    np.testing.assert_array_equal(a.view(np.uint32), b.view(np.uint32))
