@@ -63,10 +63,13 @@ class OPTAttention(nn.Module):
 
     def forward(self, x):
         B, T, H = x.shape
-        q = self.q_proj(x).view(B, T, self.num_heads, self.head_dim).transpose(1, 2)
+        # HuggingFace's OPT scales the query projection by head_dim^-0.5 in the model's type and runs attention
+        # with unit scaling ("original order of scaling", modeling_opt.py): for head_dim 128 the factor is not a
+        # power of two, so the order matters for bit-identity with the reference's flow
+        q = (self.q_proj(x) * self.head_dim ** -0.5).view(B, T, self.num_heads, self.head_dim).transpose(1, 2)
         k = self.k_proj(x).view(B, T, self.num_heads, self.head_dim).transpose(1, 2)
         v = self.v_proj(x).view(B, T, self.num_heads, self.head_dim).transpose(1, 2)
-        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=1.0)
         return self.out_proj(y.transpose(1, 2).reshape(B, T, H))
 
 

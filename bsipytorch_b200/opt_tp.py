@@ -244,7 +244,8 @@ class TPDecoderLayer(nn.Module):
     def _attention(self, qkv, B, T):
         Hl, nh, hd = self.h_hi - self.h_lo, self.local_heads, self.head_dim
         q, k, v = (qkv[:, i * Hl:(i + 1) * Hl].view(B, T, nh, hd).transpose(1, 2) for i in range(3))
-        attn = F.scaled_dot_product_attention(q, k, v, is_causal=True)               # [B, nh, T, hd]
+        # query scaled in the model's type, attention with unit scaling: the order HuggingFace's OPT uses
+        attn = F.scaled_dot_product_attention(q * hd ** -0.5, k, v, is_causal=True, scale=1.0)   # [B, nh, T, hd]
         return attn.transpose(1, 2).reshape(B * T, Hl)
 
     def forward_peer(self, x_loc, delta, B, T, px: "PeerExchange"):
