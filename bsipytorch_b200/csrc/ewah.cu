@@ -12,6 +12,11 @@
 //   literal w goes to (segments started at or before w) + (literals before w)
 //   RLW = run_bit | (run_len & 0xFFFFFFFF) << 1 | literal_count << 33, written when the segment
 //   closes (at the next start, or at W).
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace bsi {
@@ -262,6 +267,229 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_decode_kernel(
     for (int64_t k = o + lane; k < W; k += 32) dst[k] = 0ull;
 }
 
+// ---- the one-call encoder's own kernels -----------------------------------------------------------
+// Slices of up to 256 words (8 words per lane) are held in registers: every load of a slice is in flight at once,
+// the popcount and the size walk share one read, and the walk itself never waits for memory.
+//
+// The compress flag depends on the slice only through its popcount, and for one (W, threshold) the reference's
+// float64 expression is evaluated for every possible count once (ewah_cuts_kernel, same compress_flag, hence the
+// same roundings) and summarised by the host as "flag = count < first_zero or count > last_zero" when the flags
+// have that shape; the per-slice kernels then compare two integers instead of calling pow() twice.
+struct FlagCuts {
+    long long first_zero;   // smallest count whose flag is 0 (64 W + 1 if none)
+    long long last_zero;    // largest count whose flag is 0 (-1 if none)
+    int regular;            // 1: every count in [first_zero, last_zero] has flag 0, so the two bounds decide
+};
+
+__global__ void __launch_bounds__(1024) ewah_cuts_kernel(int64_t W, double threshold, long long* __restrict__ result) {
+    __shared__ long long s_first, s_last, s_zeros;
+    if (threadIdx.x == 0) {
+        s_first = 64 * W + 1;
+        s_last = -1;
+        s_zeros = 0;
+    }
+    __syncthreads();
+    long long first = 64 * W + 1, last = -1, zeros = 0;
+    for (long long c = threadIdx.x; c <= 64 * W; c += blockDim.x) {
+        if (!compress_flag(static_cast<u64>(c), W, threshold)) {
+            first = c < first ? c : first;
+            last = c > last ? c : last;
+            ++zeros;
+        }
+    }
+    atomicMin(&s_first, first);
+    atomicMax(&s_last, last);
+    atomicAdd(reinterpret_cast<unsigned long long*>(&s_zeros), static_cast<unsigned long long>(zeros));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        result[0] = s_first;
+        result[1] = s_last;
+        result[2] = (s_last < 0 || s_zeros == s_last - s_first + 1) ? 1 : 0;
+    }
+}
+
+__device__ __forceinline__ int flag_from(u64 count, int64_t W, double threshold, const FlagCuts& cuts) {
+    if (cuts.regular) {
+        const long long c = static_cast<long long>(count);
+        return (c < cuts.first_zero || c > cuts.last_zero) ? 1 : 0;
+    }
+    return compress_flag(count, W, threshold);
+}
+
+// encode_slice on a slice held in registers: wv[t] is this lane's word of tile t (word index 32 t + lane).
+template <bool EMIT, int TILES>
+__device__ __forceinline__ u64 encode_slice_regs(const u64 (&wv)[TILES], int64_t W, int compress,
+                                                 u64* __restrict__ out, int lane) {
+    if (!compress) {
+        if (EMIT) {
+            if (lane == 0) out[0] = static_cast<u64>(W) << 33;
+#pragma unroll
+            for (int t = 0; t < TILES; ++t) {
+                const int64_t w = t * 32 + lane;
+                if (w < W) out[1 + w] = wv[t];
+            }
+        }
+        return 1ull + static_cast<u64>(W);
+    }
+    const unsigned below = (1u << lane) - 1u;
+    u64 seg_base = 0, lit_base = 0;
+    int prev_type = 2;
+    int64_t open_w0 = 0;
+    u64 open_lit0 = 0;
+    int open_bit = 0, open_isfill = 0;
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) {
+        const int64_t tile = t * 32;
+        if (tile < W) {
+            const int64_t w = tile + lane;
+            const bool valid = w < W;
+            const u64 word = valid ? wv[t] : 1ull;
+            const int type = (word == 0ull) ? 0 : ((word == ~0ull) ? 1 : 2);
+            int left = __shfl_up_sync(0xffffffffu, type, 1);
+            if (lane == 0) left = prev_type;
+            const bool start = valid && (w == 0 || (type != 2 && type != left));
+            const bool lit = valid && type == 2;
+            const unsigned S = __ballot_sync(0xffffffffu, start);
+            const unsigned L = __ballot_sync(0xffffffffu, lit);
+            if (EMIT) {
+                const u64 lit_here = lit_base + __popc(L & below);
+                if (lit) {
+                    const u64 segs_incl = seg_base + __popc(S & (below | (1u << lane)));
+                    out[segs_incl + lit_here] = word;
+                }
+                const unsigned prior = S & below;
+                const int p = prior ? (31 - __clz(prior)) : 0;
+                const int p_type = __shfl_sync(0xffffffffu, type, p);
+                if (start && w != 0) {
+                    int64_t w0;
+                    u64 lit0, pos;
+                    int bit, isfill;
+                    if (prior) {
+                        w0 = tile + p;
+                        lit0 = lit_base + __popc(L & ((1u << p) - 1u));
+                        pos = seg_base + __popc(S & ((1u << p) - 1u)) + lit0;
+                        bit = (p_type == 1);
+                        isfill = (p_type != 2);
+                    } else {
+                        w0 = open_w0;
+                        lit0 = open_lit0;
+                        pos = (seg_base - 1) + lit0;
+                        bit = open_bit;
+                        isfill = open_isfill;
+                    }
+                    const u64 lit_count = lit_here - lit0;
+                    const u64 run_len = isfill ? (static_cast<u64>(w - w0) - lit_count) : 0ull;
+                    out[pos] = static_cast<u64>(bit) | ((run_len & 0xFFFFFFFFull) << 1) | (lit_count << 33);
+                }
+            }
+            if (S) {
+                const int p = 31 - __clz(S);
+                const int p_type = __shfl_sync(0xffffffffu, type, p);
+                open_w0 = tile + p;
+                open_lit0 = lit_base + __popc(L & ((1u << p) - 1u));
+                open_bit = (p_type == 1);
+                open_isfill = (p_type != 2);
+            }
+            seg_base += __popc(S);
+            lit_base += __popc(L);
+            const int last = (W - tile) >= 32 ? 31 : static_cast<int>(W - tile - 1);
+            prev_type = __shfl_sync(0xffffffffu, type, last);
+        }
+    }
+    if (EMIT && lane == 0 && seg_base > 0) {
+        const u64 lit_count = lit_base - open_lit0;
+        const u64 run_len = open_isfill ? (static_cast<u64>(W - open_w0) - lit_count) : 0ull;
+        out[(seg_base - 1) + open_lit0] =
+            static_cast<u64>(open_bit) | ((run_len & 0xFFFFFFFFull) << 1) | (lit_count << 33);
+    }
+    return seg_base + lit_base;
+}
+
+template <int TILES>
+__device__ __forceinline__ void load_slice(const u64* __restrict__ base, int64_t W, int lane, u64 (&wv)[TILES]) {
+#pragma unroll
+    for (int t = 0; t < TILES; ++t) {
+        const int64_t w = t * 32 + lane;
+        wv[t] = w < W ? __ldg(base + w) : 0ull;
+    }
+}
+
+// Pass 1: flag and encoded size of every slice, and the sum of the sizes of each block's 8 slices.
+// TILES = 0 walks the slice in memory (W > 256).
+template <int TILES>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_sizes_kernel(
+    const u64* __restrict__ words, int64_t S, int64_t W, double threshold, const FlagCuts cuts,
+    int32_t* __restrict__ flags, u64* __restrict__ sizes, u64* __restrict__ block_sums) {
+    __shared__ u64 wsize[kWarpsPerBlock];
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
+    u64 n = 0;
+    if (s < S) {
+        const u64* base = words + s * W;
+        u64 local = 0;
+        int flag;
+        if constexpr (TILES > 0) {
+            u64 wv[TILES];
+            load_slice<TILES>(base, W, lane, wv);
+#pragma unroll
+            for (int t = 0; t < TILES; ++t) local += static_cast<u64>(__popcll(wv[t]));
+            flag = flag_from(warp_sum_u64(local), W, threshold, cuts);
+            n = encode_slice_regs<false, TILES>(wv, W, flag, nullptr, lane);
+        } else {
+            for (int64_t w = lane; w < W; w += 32) local += static_cast<u64>(__popcll(base[w]));
+            flag = flag_from(warp_sum_u64(local), W, threshold, cuts);
+            n = encode_slice<false>(base, W, flag, nullptr, lane);
+        }
+        if (lane == 0) {
+            flags[s] = flag;
+            sizes[s] = n;
+        }
+    }
+    if (lane == 0) wsize[warp] = n;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u64 t = 0;
+#pragma unroll
+        for (int w = 0; w < kWarpsPerBlock; ++w) t += wsize[w];
+        block_sums[blockIdx.x] = t;
+    }
+}
+
+// Pass 3: offsets of the block's slices from the scanned block sums, then the streams.
+template <int TILES>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_blocks_kernel(
+    const u64* __restrict__ words, int64_t S, int64_t W, const int32_t* __restrict__ flags,
+    const u64* __restrict__ sizes, const u64* __restrict__ block_off, u64 capacity,
+    u64* __restrict__ off, u64* __restrict__ out, int32_t* __restrict__ out_len) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t s0 = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock;
+    const int64_t s = s0 + warp;
+    // every warp adds up the sizes of the block's slices before its own
+    u64 mine = (lane < kWarpsPerBlock && s0 + lane < S) ? sizes[s0 + lane] : 0ull;
+    u64 before = (lane < warp) ? mine : 0ull;
+    before = warp_sum_u64(before);
+    if (s >= S) return;
+    const u64 o = block_off[blockIdx.x] + before;
+    const u64 n_expected = __shfl_sync(0xffffffffu, mine, warp);
+    if (lane == 0) off[s] = o;
+    if (o + n_expected > capacity) {
+        if (lane == 0) out_len[s] = static_cast<int32_t>(n_expected);
+        return;
+    }
+    const u64* base = words + s * W;
+    u64 n;
+    if constexpr (TILES > 0) {
+        u64 wv[TILES];
+        load_slice<TILES>(base, W, lane, wv);
+        n = encode_slice_regs<true, TILES>(wv, W, flags[s], out + o, lane);
+    } else {
+        n = encode_slice<true>(base, W, flags[s], out + o, lane);
+    }
+    if (lane == 0) out_len[s] = static_cast<int32_t>(n);
+}
+
 inline unsigned warp_blocks(int64_t S) { return static_cast<unsigned>((S + kWarpsPerBlock - 1) / kWarpsPerBlock); }
 
 int check_sw(const char* name, const void* words, int64_t S, int64_t W) {
@@ -345,9 +573,53 @@ extern "C" int bsi_b200_ewah_decode(const uint64_t* in, const uint64_t* off, con
 }
 
 extern "C" int64_t bsi_b200_ewah_scratch_bytes(int64_t S) {
-    // counts [S] + sizes [S], both uint64.
-    return S < 0 ? 0 : 2 * S * static_cast<int64_t>(sizeof(uint64_t));
+    // sizes [S], block sums and block offsets [ceil(S / 8)] each, 3 words for the flag bounds; rounded up generously
+    return S < 0 ? 0 : (2 * S + 16) * static_cast<int64_t>(sizeof(uint64_t));
 }
+
+namespace bsi {
+namespace {
+
+// Flag bounds of one (W, threshold), computed on the device with the reference's expression the first time the pair
+// is seen and kept on the host afterwards. That first time synchronises the stream (the three numbers come back to
+// the host); while a stream is being captured nothing is cached and the kernels evaluate the expression per slice.
+int flag_cuts(int64_t W, double threshold, u64* scratch3, cudaStream_t stream, FlagCuts* out) {
+    struct Entry { int64_t W; double thr; FlagCuts cuts; };
+    static std::mutex mu;
+    static std::vector<Entry> cache;
+    out->first_zero = 0;
+    out->last_zero = -1;
+    out->regular = 0;     // "irregular": evaluate per slice
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const Entry& e : cache)
+            if (e.W == W && memcmp(&e.thr, &threshold, sizeof(double)) == 0) {
+                *out = e.cuts;
+                return BSI_OK;
+            }
+    }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+        (void)cudaGetLastError();
+        return BSI_OK;
+    }
+    ewah_cuts_kernel<<<1, 1024, 0, stream>>>(W, threshold, reinterpret_cast<long long*>(scratch3));
+    if (int rc = check_launch("ewah_encode flag bounds launch")) return rc;
+    long long h[3] = {0, -1, 0};
+    BSI_CUDA_TRY(cudaMemcpyAsync(h, scratch3, sizeof(h), cudaMemcpyDeviceToHost, stream));
+    BSI_CUDA_TRY(cudaStreamSynchronize(stream));
+    FlagCuts c;
+    c.first_zero = h[0];
+    c.last_zero = h[1];
+    c.regular = static_cast<int>(h[2]);
+    *out = c;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() < 64) cache.push_back(Entry{W, threshold, c});
+    return BSI_OK;
+}
+
+}  // namespace
+}  // namespace bsi
 
 extern "C" int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W, double threshold,
                                     void* scratch, int64_t scratch_bytes,
@@ -362,17 +634,34 @@ extern "C" int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W,
         return fail(BSI_ERR_INVALID, "ewah_encode: scratch too small or misaligned");
     if (out == nullptr || off == nullptr || out_len == nullptr || flags == nullptr || capacity < 0)
         return fail(BSI_ERR_INVALID, "ewah_encode: null pointer");
-    u64* counts = static_cast<u64*>(scratch);
-    u64* sizes = counts + S;
-    ewah_flags_kernel<true><<<warp_blocks(S), kWarpsPerBlock * 32, 0, stream>>>(
-        reinterpret_cast<const u64*>(words), S, W, threshold, counts, flags, sizes);
-    if (int rc = check_launch("ewah_encode flags launch")) return rc;
-    ewah_offsets_kernel<<<1, 1024, 0, stream>>>(sizes, S, reinterpret_cast<u64*>(off),
-                                               reinterpret_cast<u64*>(total));
+    const int64_t nb = (S + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    u64* sizes = static_cast<u64*>(scratch);
+    u64* block_sums = sizes + S;
+    u64* block_off = block_sums + nb;
+    u64* cut_words = block_off + nb;
+    FlagCuts cuts;
+    if (int rc = flag_cuts(W, threshold, cut_words, stream, &cuts)) return rc;
+    const u64* w64 = reinterpret_cast<const u64*>(words);
+    const unsigned grid = warp_blocks(S);
+#define BSI_EWAH_SIZES(T) ewah_sizes_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(w64, S, W, threshold, cuts, flags, sizes, block_sums)
+    if (W <= 32) BSI_EWAH_SIZES(1);
+    else if (W <= 64) BSI_EWAH_SIZES(2);
+    else if (W <= 128) BSI_EWAH_SIZES(4);
+    else if (W <= 256) BSI_EWAH_SIZES(8);
+    else BSI_EWAH_SIZES(0);
+#undef BSI_EWAH_SIZES
+    if (int rc = check_launch("ewah_encode sizes launch")) return rc;
+    ewah_offsets_kernel<<<1, 1024, 0, stream>>>(block_sums, nb, block_off, reinterpret_cast<u64*>(total));
     if (int rc = check_launch("ewah_encode offsets launch")) return rc;
-    ewah_emit_kernel<<<warp_blocks(S), kWarpsPerBlock * 32, 0, stream>>>(
-        reinterpret_cast<const u64*>(words), S, W, flags, reinterpret_cast<const u64*>(off), sizes,
-        static_cast<u64>(capacity), reinterpret_cast<u64*>(out), out_len);
+#define BSI_EWAH_EMIT(T) ewah_emit_blocks_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                     \
+        w64, S, W, flags, sizes, block_off, static_cast<u64>(capacity), reinterpret_cast<u64*>(off),                \
+        reinterpret_cast<u64*>(out), out_len)
+    if (W <= 32) BSI_EWAH_EMIT(1);
+    else if (W <= 64) BSI_EWAH_EMIT(2);
+    else if (W <= 128) BSI_EWAH_EMIT(4);
+    else if (W <= 256) BSI_EWAH_EMIT(8);
+    else BSI_EWAH_EMIT(0);
+#undef BSI_EWAH_EMIT
     return check_launch("ewah_encode emit launch");
 }
 
