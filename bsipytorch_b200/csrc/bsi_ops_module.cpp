@@ -140,6 +140,17 @@ T* from_capsule(const py::capsule& cap, const char* name) {
     return reinterpret_cast<T*>(cap.get_pointer());
 }
 
+// The device a call works on: its first CUDA tensor's, else the current one. Every entry point switches to it for
+// its duration (c10::cuda::CUDAGuard), so that allocations, the current stream and the library's per-device caches
+// all mean the device the data lives on, whichever device is current in the caller.
+at::Device work_device(const at::Tensor& t) {
+    return t.is_cuda() ? t.device() : at::Device(at::kCUDA, c10::cuda::current_device());
+}
+void same_device(const at::Tensor& a, const at::Tensor& b, const char* what) {
+    TORCH_CHECK(!a.defined() || !b.defined() || !a.is_cuda() || !b.is_cuda() || a.device() == b.device(), what,
+                ": tensors live on different CUDA devices (", a.device(), " and ", b.device(), ")");
+}
+
 uint64_t g_last_quantize_ns = 0, g_last_pack_ns = 0, g_last_total_ns = 0;
 
 // Quantise + pack `x` ([rows, d], f32/f16/bf16, CPU or CUDA) in one kernel.
@@ -149,7 +160,8 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
                  bool lean = false) {
     TORCH_CHECK(input.dim() == 2, "expects 2D tensor [rows, d]");
     check_clip();
-    const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
+    const auto dev = work_device(input);
+    c10::cuda::CUDAGuard guard(dev);
     at::Tensor x = input.detach();
     if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
         x = x.to(at::kFloat);
@@ -222,7 +234,8 @@ int variable_slices(uint64_t max_abs) {
 // (|v| <= 127); anything larger is refused rather than computed some other way.
 PackedBatch pack_variable(const at::Tensor& input, int decimal_places, bool for_keys) {
     TORCH_CHECK(input.dim() == 2, "expects 2D tensor [rows, d]");
-    const auto dev = at::Device(at::kCUDA, c10::cuda::current_device());
+    const auto dev = work_device(input);
+    c10::cuda::CUDAGuard guard(dev);
     at::Tensor x = input.detach();
     if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
         x = x.to(at::kFloat);
@@ -388,6 +401,7 @@ struct EwahStream {
 EwahStream ewah_encode(const at::Tensor& words2d, double threshold) {
     TORCH_CHECK(words2d.dim() == 2 && words2d.scalar_type() == at::kLong && words2d.is_cuda(),
                 "words must be a CUDA int64 tensor [S, W]");
+    c10::cuda::CUDAGuard guard(words2d.device());
     auto w = words2d.contiguous();
     const int64_t S = w.size(0), W = w.size(1);
     auto o64 = at::TensorOptions().dtype(at::kLong).device(w.device());
@@ -417,6 +431,8 @@ EwahStream ewah_encode(const at::Tensor& words2d, double threshold) {
 
 at::Tensor ewah_decode(const EwahStream& e, int64_t W) {
     const int64_t S = e.off.size(0);
+    c10::cuda::CUDAGuard guard(e.off.device());
+    same_device(e.off, e.stream, "ewah_decode");
     auto out = at::empty({S, W}, at::TensorOptions().dtype(at::kLong).device(e.off.device()));
     if (S > 0) {
         check_status(bsi_b200_ewah_decode(reinterpret_cast<const uint64_t*>(e.stream.data_ptr<int64_t>()),
@@ -449,6 +465,8 @@ py::tuple build_bsi_query_cuda_hybrid(torch::Tensor q, int decimalPlaces, double
 // ---- dot ------------------------------------------------------------------------------------------
 py::tuple run_dot(const PackedBatch& qb, const PrebuiltBSIKeysCUDA& keys, bool want_iacc, at::Tensor* iacc_out) {
     const int64_t Q = qb.rows, R = keys.num_keys;
+    same_device(qb.q8, keys.b.q8, "queries and keys");
+    c10::cuda::CUDAGuard guard(keys.b.q8.device());
     TORCH_CHECK(Q > 0 && qb.S > 0 && qb.W > 0, "Empty query batch");
     TORCH_CHECK(qb.W == keys.b.W, "Word count mismatch between query batch and keys");
     TORCH_CHECK(R > 0, "Empty keys");
@@ -632,6 +650,8 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
                               int decimalPlaces) {
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
+    same_device(x2d, keys->b.q8, "activations and keys");
+    c10::cuda::CUDAGuard guard(x2d.device());
     const int engine = engine_from_env();
     // two-digit variable-slice queries need two dots and a combine: they take the unfused route below
     const bool fused = (engine == BSI_ENGINE_AUTO || engine == BSI_ENGINE_TCGEN05) && bits_queries() > 0;
@@ -681,6 +701,9 @@ void pack_queries_into(torch::Tensor x2d, torch::Tensor q8, torch::Tensor scales
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [rows, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
     check_clip();
+    same_device(x2d, q8, "pack_queries_into");
+    same_device(x2d, scales, "pack_queries_into");
+    c10::cuda::CUDAGuard guard(x2d.device());
     TORCH_CHECK(chunk_scale_enabled(), "pack_queries_into needs BSI_FIXED_CHUNK_SCALE=1");
     at::Tensor x = x2d.detach();
     if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
@@ -705,6 +728,9 @@ at::Tensor linear_from_packed(torch::Tensor q8, torch::Tensor scales, py::capsul
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
+    same_device(q8, scales, "packed activations and scales");
+    same_device(q8, keys->b.q8, "packed activations and keys");
+    c10::cuda::CUDAGuard guard(q8.device());
     const int64_t Q = q8.size(0), R = keys->num_keys, chunks = keys->b.chunks;
     TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
     TORCH_CHECK(q8.size(1) == chunks * 256, "Word count mismatch between query batch and keys");
@@ -770,6 +796,7 @@ void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t
     require_fixed_queries("pack_queries_multi");
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
     TORCH_CHECK(!q8_ptrs.empty() && !scale_ptrs.empty(), "destination lists must not be empty");
+    c10::cuda::CUDAGuard guard(x2d.device());   // raw destinations: the caller's own or peer mappings of this device
     check_clip();
     TORCH_CHECK(chunk_scale_enabled(), "pack_queries_multi needs BSI_FIXED_CHUNK_SCALE=1");
     at::Tensor x = x2d.detach();
@@ -794,6 +821,9 @@ void linear_from_packed_scatter(torch::Tensor q8, torch::Tensor scales, py::caps
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
+    same_device(q8, scales, "packed activations and scales");
+    same_device(q8, keys->b.q8, "packed activations and keys");
+    c10::cuda::CUDAGuard guard(q8.device());
     const int64_t Q = q8.size(0), R = keys->num_keys, chunks = keys->b.chunks;
     TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
     TORCH_CHECK(q8.size(1) == chunks * 256, "Word count mismatch between query batch and keys");
@@ -833,6 +863,9 @@ void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::caps
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
     TORCH_CHECK(q8_ptrs.size() == scale_ptrs.size() && !q8_ptrs.empty(), "destination lists must match");
+    same_device(q8, scales, "packed activations and scales");
+    same_device(q8, keys->b.q8, "packed activations and keys");
+    c10::cuda::CUDAGuard guard(q8.device());
     const int64_t Q = q8.size(0), R = keys->num_keys, chunks = keys->b.chunks;
     TORCH_CHECK(Q > 0 && R > 0, "Empty queries or keys");
     TORCH_CHECK(q8.size(1) == chunks * 256, "Word count mismatch between query batch and keys");
@@ -874,6 +907,9 @@ at::Tensor add_layernorm_pack(torch::Tensor x, c10::optional<torch::Tensor> delt
                     bias.is_contiguous() && weight.numel() == x.size(1) && bias.numel() == x.size(1),
                 "LayerNorm weight / bias must match x");
     TORCH_CHECK(!q8_ptrs.empty() && !scale_ptrs.empty(), "destination lists must not be empty");
+    same_device(x, weight, "add_layernorm_pack");
+    same_device(x, bias, "add_layernorm_pack");
+    c10::cuda::CUDAGuard guard(x.device());
     check_clip();
     TORCH_CHECK(chunk_scale_enabled(), "add_layernorm_pack needs BSI_FIXED_CHUNK_SCALE=1");
     const void* dptr = nullptr;

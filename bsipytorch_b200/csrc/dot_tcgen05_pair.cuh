@@ -42,6 +42,10 @@ constexpr int kEpiWarps = 8;
 constexpr int kFirstEpiWarp = 4;
 constexpr int kRegsLow = 40;
 constexpr int kRegsHigh = 232;
+// setmaxnreg.inc draws only on what setmaxnreg.dec returned to the CTA's own pool (threads x registers per thread at
+// launch, the latter being 65536 / threads rounded down to a multiple of 8); an increase beyond the pool never returns.
+static_assert(kFirstEpiWarp * 32 * kRegsLow + kEpiWarps * 32 * kRegsHigh <= kThreads * ((65536 / kThreads) / 8 * 8),
+              "register budget of the warp groups exceeds the CTA's pool");
 constexpr long long kWait = 500000000ll;  // ~0.25 s; real waits are microseconds
 
 constexpr int kSmemLimit = 232448;   // 227 KB: the most dynamic shared memory one CTA can opt in to

@@ -14,6 +14,8 @@
 //   closes (at the next start, or at W).
 #include <string.h>
 
+#include <atomic>
+
 #include <mutex>
 #include <vector>
 
@@ -682,7 +684,8 @@ namespace {
 // On the host the array's name is only a handle for the runtime, not a device address; the address
 // that kernels may dereference is looked up once per device, with that device current.
 int static_scratch_address(u64** out) {
-    static u64* cached[64] = {nullptr};
+    // one slot per device; host threads that race on a first call store the same address, hence relaxed atomics
+    static std::atomic<u64*> cached[64];
     int dev = 0;
     BSI_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) {
@@ -691,13 +694,15 @@ int static_scratch_address(u64** out) {
         *out = static_cast<u64*>(p);
         return BSI_OK;
     }
-    if (cached[dev] == nullptr) {
+    u64* addr = cached[dev].load(std::memory_order_relaxed);
+    if (addr == nullptr) {
         void* p = nullptr;
         BSI_CUDA_TRY(cudaGetSymbolAddress(&p, g_ewah_static_scratch));
         if (p == nullptr) return fail(BSI_ERR_CUDA, "ewah_encode_static: cudaGetSymbolAddress returned null");
-        cached[dev] = static_cast<u64*>(p);
+        addr = static_cast<u64*>(p);
+        cached[dev].store(addr, std::memory_order_relaxed);
     }
-    *out = cached[dev];
+    *out = addr;
     return BSI_OK;
 }
 

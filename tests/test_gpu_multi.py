@@ -101,3 +101,35 @@ def test_tensor_parallel_opt_equals_single_gpu(tmp_path, exchange, microbatches)
     assert res["status"] == 0, "a bounded device-side wait gave up"
     assert res["finite"] and res["tokens_equal"] and res["graph_equal"]
     assert res["max_abs_diff"] <= 2.0 ** -9, res
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_entry_points_work_on_the_tensors_device_not_the_current_one():
+    """Keys and activations on cuda:1 while cuda:0 is current: every entry point switches to the data's device
+    (allocations, stream, per-device caches), gives cuda:0's results bit for bit, and refuses operands that
+    live on different devices."""
+    import bsipytorch_b200
+    ops = bsipytorch_b200.bsi_ops
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(300, 768, generator=g).to(torch.float16)
+    w = torch.randn(640, 768, generator=g) * 0.02
+    b = torch.randn(640, generator=g)
+    outs, ys, streams = [], [], []
+    for dev in ("cuda:0", "cuda:1"):
+        torch.cuda.set_device(0)
+        keys = ops.build_bsi_keys_cuda(w.to(dev), 2, 0.2)[0]
+        cap = ops.build_bsi_queries_cuda_batch_packed(x.to(dev), 2, 0.2)
+        out = ops.batch_dot_product_multiquery_cuda_batch_caps(cap, keys)[0]
+        y = ops.bsi_linear_forward(x.to(dev), keys, b.to(dev), 2)
+        words = ops.debug_query_batch_tensors(cap)["words"]
+        enc = ops.ewah_encode_words(words.reshape(-1, words.shape[-1]), 0.5)
+        assert str(out.device) == dev and str(y.device) == dev and str(enc[0].device) == dev
+        torch.cuda.synchronize(dev)
+        outs.append(out.cpu()), ys.append(y.cpu()), streams.append(enc[0].cpu())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(ys[0], ys[1]) and torch.equal(streams[0], streams[1])
+    keys0 = ops.build_bsi_keys_cuda(w.to("cuda:0"), 2, 0.2)[0]
+    with pytest.raises(RuntimeError, match="different CUDA devices"):
+        ops.bsi_linear_forward(x.to("cuda:1"), keys0, None, 2)
+    cap1 = ops.build_bsi_queries_cuda_batch_packed(x.to("cuda:1"), 2, 0.2)
+    with pytest.raises(RuntimeError, match="different CUDA devices"):
+        ops.batch_dot_product_multiquery_cuda_batch_caps(cap1, keys0)

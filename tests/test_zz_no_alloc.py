@@ -60,6 +60,17 @@ def test_static_scratch_encoder_matches_regular_encoder_twice():
         assert torch.equal(H.ewah_decode(got[0], got[1], got[2], W), words)
 
 
+def test_static_scratch_encoder_at_its_slice_limit():
+    # exactly as many slices as the array holds: the counts fill their half, the sizes end at the array's last word
+    S, W = capi.EWAH_STATIC_MAX_SLICES, 4
+    words = _words(S, W, 3)
+    want = H.ewah_encode(words, 0.5)
+    got = _encode_static(words, 0.5)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert torch.equal(H.ewah_decode(got[0], got[1], got[2], W), words)
+
+
 def test_static_scratch_encoder_rejects_oversized_requests():
     L = capi.lib()
     w = torch.zeros(4, 4, dtype=torch.int64, device=DEV)
