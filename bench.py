@@ -5,13 +5,16 @@
 
 Default workload (fc1): one step = one pass of the hot path over one batch, the fixed76 chunk-scale BSI dot of
 the FC1-like shape (Q=512 fp16 activations x R=8192 keys x D=2048; fc2: Q=512 x R=2048 x D=8192), keys prebuilt,
-queries packed. ``value`` is effective TOPS = 2*Q*R*D / time with every operand resident in HBM; ``e2e`` is the
-same metric through the public ``bsi_ops`` entry points starting from pinned HOST activations and ending with the
-float32 result back on the host.
+queries packed. The K-step region is timed ``--repeats`` times: ``value`` is effective TOPS = 2*Q*R*D / time of the
+MEDIAN region with every operand resident in HBM; ``timing`` holds best and worst, SM cycles per step and the time
+of a single launch after an L2 flush; ``sustained`` a leg of back-to-back replays lasting ``--sustained-seconds``.
+``e2e`` is the same metric through the public ``bsi_ops`` entry points starting from pinned HOST activations and
+ending with the float32 result back on the host. The fc1 line also carries ``fc2`` (the second dot shape, N = 1)
+and ``opt_6_7b`` (tokens/s of the tensor-parallel OPT-6.7B forward on the same ranks) unless ``--extras 0``.
 
 N > 1 (launched under torchrun, one rank per GPU): the keys are sharded along R, every rank owns an R-row shard
 of the same size (weak scaling) and there is no data-path collective in the dot itself; timing is the max over
-ranks.
+ranks. The ``opt_6_7b`` block is strong scaling: the same batch over R-sharded keys with the activation exchange.
 
 Other workloads: ``pack`` / ``pack-lean`` / ``ewah`` time the HBM-bound kernels of the path (GB/s against the
 measured copy bandwidth); ``opt-125m`` / ``opt-6.7b`` time the OPT forward with every q/k/v/out/fc1/fc2 linear as
