@@ -25,6 +25,7 @@ SIGNATURES = {
     "bsi_b200_version": (_i32, []),
     "bsi_b200_device_status": (_i32, [C.POINTER(_i32)]),
     "bsi_b200_quantize_pack": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _i64, _vp]),
+    "bsi_b200_quantize_pack_clip": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _i64, _vp]),
     "bsi_b200_decimal_absmax": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _vp, _vp]),
     "bsi_b200_pack_plain": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
     "bsi_b200_recombine_i8": (_i32, [_vp, _i64, _i32, _i64, _vp, _i64, _vp]),

@@ -49,9 +49,18 @@ int bits_queries() { return fixed_bits("BSI_FIXED_BITS_QUERIES", 7); }
 int bits_keys() { return fixed_bits("BSI_FIXED_BITS_KEYS", 6); }
 bool chunk_scale_enabled() { return env_int("BSI_FIXED_CHUNK_SCALE", 1) != 0; }
 bool profile_enabled() { return env_int("BSI_PROFILE", 0) != 0; }
-void check_clip() {
+// BSI_FIXED_CLIP_K (bsi_vector_cuda.cpp:295-307): > 0 caps the magnitude that selects a group's shift at
+// clip_k * mean |v|. The reference reads it once per process; here it is read per call like the other switches.
+float clip_k_from_env() {
     const char* s = std::getenv("BSI_FIXED_CLIP_K");
-    TORCH_CHECK(!(s && std::strtof(s, nullptr) > 0.0f), "BSI_FIXED_CLIP_K > 0 (outlier clipping) is not supported");
+    const float v = s ? std::strtof(s, nullptr) : 0.0f;
+    return v > 0.0f ? v : 0.0f;
+}
+// The builders honour the variable; the fused additions below (single-call layer, packers that write into
+// exchange buffers, re-quantising epilogue) have no clipping variant and refuse to run with it.
+void check_clip(const char* what) {
+    TORCH_CHECK(!(clip_k_from_env() > 0.0f), what, " does not implement BSI_FIXED_CLIP_K > 0 (outlier clipping); "
+                "use the build_bsi_* entry points");
 }
 int engine_from_env() {
     const char* s = std::getenv("BSI_B200_ENGINE");
@@ -159,7 +168,7 @@ uint64_t g_last_quantize_ns = 0, g_last_pack_ns = 0, g_last_total_ns = 0;
 PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chunk_mode, bool profile,
                  bool lean = false) {
     TORCH_CHECK(input.dim() == 2, "expects 2D tensor [rows, d]");
-    check_clip();
+    const float clip_k = clip_k_from_env();
     const auto dev = work_device(input);
     c10::cuda::CUDAGuard guard(dev);
     at::Tensor x = input.detach();
@@ -198,12 +207,12 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
         cudaEventCreate(&e1);
         cudaEventRecord(e0, stream.stream());
     }
-    check_status(bsi_b200_quantize_pack(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, bits,
-                                        chunk_mode ? 1 : 0,
-                                        lean ? nullptr : reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
-                                        b.scales.data_ptr<float>(), nullptr, b.q8.data_ptr<int8_t>(), ld8,
-                                        current_stream()),
-                 "bsi_b200_quantize_pack");
+    check_status(bsi_b200_quantize_pack_clip(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, bits,
+                                             chunk_mode ? 1 : 0, clip_k,
+                                             lean ? nullptr : reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
+                                             b.scales.data_ptr<float>(), nullptr, b.q8.data_ptr<int8_t>(), ld8,
+                                             current_stream()),
+                 "bsi_b200_quantize_pack_clip");
     if (profile) {
         cudaEventRecord(e1, stream.stream());
         cudaEventSynchronize(e1);
@@ -700,7 +709,7 @@ void pack_queries_into(torch::Tensor x2d, torch::Tensor q8, torch::Tensor scales
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [rows, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
-    check_clip();
+    check_clip("pack_queries_into");
     same_device(x2d, q8, "pack_queries_into");
     same_device(x2d, scales, "pack_queries_into");
     c10::cuda::CUDAGuard guard(x2d.device());
@@ -797,7 +806,7 @@ void pack_queries_multi(torch::Tensor x2d, std::vector<int64_t> q8_ptrs, int64_t
     TORCH_CHECK(x2d.dim() == 2 && x2d.is_cuda(), "x must be a 2D CUDA tensor");
     TORCH_CHECK(!q8_ptrs.empty() && !scale_ptrs.empty(), "destination lists must not be empty");
     c10::cuda::CUDAGuard guard(x2d.device());   // raw destinations: the caller's own or peer mappings of this device
-    check_clip();
+    check_clip("pack_queries_multi");
     TORCH_CHECK(chunk_scale_enabled(), "pack_queries_multi needs BSI_FIXED_CHUNK_SCALE=1");
     at::Tensor x = x2d.detach();
     if (!(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16))
@@ -859,6 +868,7 @@ void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::caps
                                 std::vector<int64_t> q8_ptrs, int64_t ld8, std::vector<int64_t> scale_ptrs,
                                 int64_t scale_ld) {
     require_fixed_queries("linear_from_packed_requant");
+    check_clip("linear_from_packed_requant");
     auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(keyset_cuda_cap, "PrebuiltBSIKeysCUDA");
     TORCH_CHECK(q8.dim() == 2 && q8.is_cuda() && q8.scalar_type() == at::kChar && q8.stride(1) == 1, "q8 must be int8 [Q, d]");
     TORCH_CHECK(scales.is_cuda() && scales.scalar_type() == at::kFloat && scales.is_contiguous(), "scales must be contiguous float32");
@@ -910,7 +920,7 @@ at::Tensor add_layernorm_pack(torch::Tensor x, c10::optional<torch::Tensor> delt
     same_device(x, weight, "add_layernorm_pack");
     same_device(x, bias, "add_layernorm_pack");
     c10::cuda::CUDAGuard guard(x.device());
-    check_clip();
+    check_clip("add_layernorm_pack");
     TORCH_CHECK(chunk_scale_enabled(), "add_layernorm_pack needs BSI_FIXED_CHUNK_SCALE=1");
     const void* dptr = nullptr;
     at::Tensor d;

@@ -86,6 +86,31 @@ __device__ __forceinline__ int shift_for(u64 max_abs, int bits) {
     return shift > 62 ? 62 : shift;
 }
 
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Shift selection with outlier clipping (bsi_cuda_kernels_quant.cuh:82-108, BSI_FIXED_CLIP_K > 0): the width comes
+// from min(max |v|, clip_k * mean |v|) instead of max |v|, so a few extreme values no longer push the whole group
+// to a coarse shift; they saturate at the clamp instead. `sum_abs` is the sum of the group's |v| (integers, so any
+// summation order gives the same double below 2^53), `count` its number of elements.
+__device__ __forceinline__ int shift_for_clipped(u64 max_abs, double sum_abs, int count, int bits, float clip_k) {
+    int width = 0;
+    if (count > 0) {
+        double effective = static_cast<double>(max_abs);
+        const double clip_max = (sum_abs / static_cast<double>(count)) * static_cast<double>(clip_k);
+        if (clip_max < effective) effective = clip_max;
+        if (effective > 0.0) (void)frexp(effective, &width);
+    } else {
+        width = max_abs ? (64 - __clzll(static_cast<long long>(max_abs))) : 0;
+    }
+    int shift = width - (bits - 1);
+    shift = shift < 0 ? 0 : shift;
+    return shift > 62 ? 62 : shift;
+}
+
 // Transposes the 8x8 bit matrix held in x (row e = byte e, LSB first): afterwards bit e of
 // byte s is the former bit s of byte e.
 __device__ __forceinline__ u64 transpose8x8(u64 x) {
@@ -188,21 +213,29 @@ __device__ __forceinline__ void generic_unit(const T* __restrict__ x, int64_t un
                                              double dec_scale, uint32_t dec_mult, int bits, int64_t chunks, int64_t W,
                                              u64* __restrict__ words, float* __restrict__ scales,
                                              int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8,
-                                             bool vec, int lane) {
+                                             bool vec, int lane, float clip_k = 0.0f) {
     const int64_t row = unit / chunks;
     const int64_t chunk = unit - row * chunks;
     float f[8];
     load8<T>(x + row * ldx, chunk * 256 + lane * 8, D, vec, f);
     long long v[8];
     u64 mx = 0;
+    double sum = 0.0;
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         v[e] = decimal_round(f[e], dec_scale, dec_mult);
         const u64 a = uabs(v[e]);
         mx = a > mx ? a : mx;
+        sum += static_cast<double>(a);     // elements beyond D were loaded as 0
     }
     mx = warp_max_u64(mx);
-    const int shift = shift_for(mx, bits);
+    int shift;
+    if (clip_k > 0.0f) {
+        const int64_t left = D - chunk * 256;
+        shift = shift_for_clipped(mx, warp_sum_f64(sum), static_cast<int>(left < 256 ? left : 256), bits, clip_k);
+    } else {
+        shift = shift_for(mx, bits);
+    }
     if (lane == 0) {
         if (scales != nullptr) scales[unit] = static_cast<float>(1ull << shift);
         if (shifts != nullptr) shifts[unit] = shift;
@@ -216,13 +249,13 @@ template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_chunk_generic_kernel(
     const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
     int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
-    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok) {
+    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok, float clip_k) {
     const int lane = threadIdx.x & 31;
     const int64_t total = rows * chunks;
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * 8)
         generic_unit<T>(x, unit, D, ldx, dec_scale, dec_mult, bits, chunks, W, words, scales, shifts, q8, ld8,
-                        vec_ok != 0, lane);
+                        vec_ok != 0, lane, clip_k);
 }
 
 // Fast path of one chunk: true when the chunk was quantised and stored, false when it needs the generic
@@ -727,14 +760,16 @@ template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
     const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
     int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
-    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok) {
+    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok, float clip_k) {
     __shared__ u64 warp_max[8];
+    __shared__ double warp_sum[8];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int64_t row = blockIdx.x;
     const T* xr = x + row * ldx;
 
     u64 mx = 0;
+    double sum = 0.0;
     for (int64_t chunk = warp; chunk < chunks; chunk += 8) {
         float f[8];
         load8<T>(xr, chunk * 256 + lane * 8, D, vec_ok != 0, f);
@@ -742,15 +777,24 @@ __global__ void __launch_bounds__(256) quantize_pack_row_kernel(
         for (int e = 0; e < 8; ++e) {
             const u64 a = uabs(decimal_round(f[e], dec_scale, dec_mult));
             mx = a > mx ? a : mx;
+            if (clip_k > 0.0f) sum += static_cast<double>(a);
         }
     }
     mx = warp_max_u64(mx);
-    if (lane == 0) warp_max[warp] = mx;
+    if (clip_k > 0.0f) sum = warp_sum_f64(sum);
+    if (lane == 0) {
+        warp_max[warp] = mx;
+        warp_sum[warp] = sum;
+    }
     __syncthreads();
     mx = warp_max[0];
+    sum = warp_sum[0];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) mx = warp_max[i] > mx ? warp_max[i] : mx;
-    const int shift = shift_for(mx, bits);
+    for (int i = 1; i < 8; ++i) {
+        mx = warp_max[i] > mx ? warp_max[i] : mx;
+        sum += warp_sum[i];
+    }
+    const int shift = clip_k > 0.0f ? shift_for_clipped(mx, sum, static_cast<int>(D), bits, clip_k) : shift_for(mx, bits);
     if (threadIdx.x == 0) {
         if (scales != nullptr) scales[row] = static_cast<float>(1ull << shift);
         if (shifts != nullptr) shifts[row] = shift;
@@ -863,6 +907,7 @@ struct ChunkArgs {
     int8_t* q8;
     int vec_ok;
     cudaStream_t stream;
+    float clip_k;
 };
 
 template <typename T, bool kDense, bool kWords, bool kQ8>
@@ -886,14 +931,14 @@ int launch_chunk_fast(const T* x, const ChunkArgs& a) {
 }
 
 // Chunk mode: the fast kernel when its preconditions hold (10^dp small enough for the input type, scales
-// wanted, every offset below 2^31), else the generic kernel.
+// wanted, every offset below 2^31, no outlier clipping), else the generic kernel.
 template <typename T>
 int launch_chunk(const T* x, const ChunkArgs& a) {
     int64_t widest = a.chunks * 256;
     if (a.ldx > widest) widest = a.ldx;
     if (a.q8 != nullptr && a.ld8 > widest) widest = a.ld8;
     const uint32_t mult_limit = sizeof(T) == 2 ? 1000u : 127u;
-    const bool fast = a.dec_mult != 0u && a.dec_mult <= mult_limit && a.scales != nullptr &&
+    const bool fast = a.dec_mult != 0u && a.dec_mult <= mult_limit && a.scales != nullptr && !(a.clip_k > 0.0f) &&
                       a.rows * widest < (1ll << 31) && (a.words != nullptr || a.q8 != nullptr);
     if (!fast) {
         int64_t blocks = (a.rows * a.chunks + 7) / 8;
@@ -901,7 +946,7 @@ int launch_chunk(const T* x, const ChunkArgs& a) {
         blocks = blocks < cap ? blocks : cap;
         quantize_pack_chunk_generic_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
             x, a.rows, a.D, a.ldx, a.dec_scale, a.dec_mult, a.bits, a.chunks, a.W, a.words, a.scales, a.shifts, a.q8,
-            a.ld8, a.vec_ok);
+            a.ld8, a.vec_ok, a.clip_k);
         return BSI_OK;
     }
     const bool dense = a.vec_ok && a.ldx == a.D && (a.D & 255) == 0 && (a.q8 == nullptr || a.ld8 == a.D);
@@ -922,6 +967,14 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
                                       int decimal_places, int bits, int chunk_mode,
                                       uint64_t* words, float* scales, int32_t* shifts,
                                       int8_t* q8, int64_t ld8, bsi_stream_t stream_) {
+    return bsi_b200_quantize_pack_clip(x, dtype, rows, D, ldx, decimal_places, bits, chunk_mode, 0.0f, words, scales,
+                                       shifts, q8, ld8, stream_);
+}
+
+extern "C" int bsi_b200_quantize_pack_clip(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                                           int decimal_places, int bits, int chunk_mode, float clip_k,
+                                           uint64_t* words, float* scales, int32_t* shifts,
+                                           int8_t* q8, int64_t ld8, bsi_stream_t stream_) {
     using namespace bsi;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (rows < 0 || D < 0 || ldx < D) return fail(BSI_ERR_INVALID, "quantize_pack: bad rows/D/ldx");
@@ -948,7 +1001,7 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
     u64* w = reinterpret_cast<u64*>(words);
 
     if (chunk_mode) {
-        ChunkArgs a{rows, D, ldx, ld8, chunks, W, dec_scale, dec_mult, bits, w, scales, shifts, q8, vec_ok, stream};
+        ChunkArgs a{rows, D, ldx, ld8, chunks, W, dec_scale, dec_mult, bits, w, scales, shifts, q8, vec_ok, stream, clip_k};
         int rc;
         if (dtype == BSI_DTYPE_F32) rc = launch_chunk<float>(static_cast<const float*>(x), a);
         else if (dtype == BSI_DTYPE_F16) rc = launch_chunk<__half>(static_cast<const __half*>(x), a);
@@ -958,7 +1011,7 @@ extern "C" int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, in
         if (rows > 0x7fffffffll) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack: too many rows for one launch");
 #define BSI_LAUNCH_ROW(T)                                                                              \
     quantize_pack_row_kernel<T><<<static_cast<unsigned>(rows), 256, 0, stream>>>(                      \
-        static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales, shifts, q8, ld8, vec_ok)
+        static_cast<const T*>(x), rows, D, ldx, dec_scale, dec_mult, bits, chunks, W, w, scales, shifts, q8, ld8, vec_ok, clip_k)
         if (dtype == BSI_DTYPE_F32) BSI_LAUNCH_ROW(float);
         else if (dtype == BSI_DTYPE_F16) BSI_LAUNCH_ROW(__half);
         else BSI_LAUNCH_ROW(__nv_bfloat16);

@@ -83,6 +83,15 @@ int bsi_b200_quantize_pack(const void* x, int dtype, int64_t rows, int64_t D, in
                            uint64_t* words, float* scales, int32_t* shifts,
                            int8_t* q8, int64_t ld8, bsi_stream_t stream);
 
+/* The same with the reference's outlier clipping (BSI_FIXED_CLIP_K, bsi_cuda_kernels_quant.cuh:82-108,
+ * bsi_vector_cuda.cpp:295-307): for clip_k > 0 the shift of a group comes from
+ * min(max |v|, clip_k * mean |v|), and values beyond the range saturate at the clamp. clip_k <= 0 is
+ * bsi_b200_quantize_pack. */
+int bsi_b200_quantize_pack_clip(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                                int decimal_places, int bits, int chunk_mode, float clip_k,
+                                uint64_t* words, float* scales, int32_t* shifts,
+                                int8_t* q8, int64_t ld8, bsi_stream_t stream);
+
 /* ---- variable-slice mode (the reference's default when no BSI_FIXED_BITS* variable is set) ------
  * The decimal integers v = half_away(double(float(x)) * 10^decimal_places) are sliced as they are,
  * without a shift; the number of slices follows from the largest |v| (bit_width(max|v|) + 2, at least

@@ -193,7 +193,7 @@ def scale_inv(decimal_places: int) -> np.float32:
 
 
 def fixed_dot(xq, xk, decimal_places: int = 2, bits_q: int = 7, bits_k: int = 6,
-              want_iacc: bool = False, via: str = "i8"):
+              want_iacc: bool = False, via: str = "i8", clip_k: float = 0.0, chunk_scale: bool = True):
     """End to end: queries xq [Q, D], keys xk [R, D] (float32) -> out [Q, R] float32.
 
     Queries get per-256-element chunk scales when ceil(D/64) is a multiple of 4, else a
@@ -202,9 +202,9 @@ def fixed_dot(xq, xk, decimal_places: int = 2, bits_q: int = 7, bits_k: int = 6,
     xk = np.ascontiguousarray(xk, np.float32)
     D = xq.shape[1]
     W = max(1, (D + 63) // 64)
-    chunk = (W % 4 == 0)
-    qa = quantize_pack(xq, decimal_places, bits_q, chunk)
-    kb = quantize_pack(xk, decimal_places, bits_k, False)
+    chunk = chunk_scale and (W % 4 == 0)          # BSI_FIXED_CHUNK_SCALE=0 gives one scale per query row
+    qa = quantize_pack(xq, decimal_places, bits_q, chunk, clip_k)
+    kb = quantize_pack(xk, decimal_places, bits_k, False, clip_k)
     Bw = slice_weights(bits_k, kb["scales"])
     si = scale_inv(decimal_places)
     if via == "popc":

@@ -53,7 +53,7 @@ def _dtype_code(x):
     return {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[x.dtype]
 
 
-def pack_queries_chunk(x, decimal_places=2, bits=7):
+def pack_queries_chunk(x, decimal_places=2, bits=7, clip_k=0.0):
     """Reference query builder, chunk-scale mode. Returns (words[Q,bits,W] int64, shifts, scales)."""
     L = lib()
     x = x.contiguous()
@@ -67,14 +67,14 @@ def pack_queries_chunk(x, decimal_places=2, bits=7):
     dec = C.c_double(10.0 ** decimal_places)
     L.launch_compute_chunk_shift_scale_from_input(
         _p(x), C.c_int(_dtype_code(x)), C.c_int64(Q), C.c_int64(d), C.c_int(chunks), dec, C.c_int(bits),
-        C.c_float(0.0), _p(shifts), _p(scales), _stream())
+        C.c_float(clip_k), _p(shifts), _p(scales), _stream())
     L.launch_quantize_shift_pack_chunk_batch(
         _p(x), C.c_int(_dtype_code(x)), C.c_int64(Q), C.c_int64(d), C.c_int(chunks), C.c_int(bits), C.c_int(W),
         C.c_ulonglong((1 << bits) - 1), dec, C.c_int(bits), _p(shifts), _p(words), _stream())
     return words, shifts, scales
 
 
-def pack_rows(x, decimal_places=2, bits=6):
+def pack_rows(x, decimal_places=2, bits=6, clip_k=0.0):
     """Reference fixed-bit per-row builder (the key path). Returns (words, shifts, scales, ints)."""
     L = lib()
     x = x.contiguous()
@@ -87,7 +87,7 @@ def pack_rows(x, decimal_places=2, bits=6):
     words = torch.zeros(R, bits, W, dtype=torch.int64, device=dev)
     L.launch_quantize_round_to_int64_batch(_p(x), C.c_int(_dtype_code(x)), C.c_int64(R), C.c_int64(d),
                                            C.c_double(10.0 ** decimal_places), _p(ints), _stream())
-    L.launch_compute_row_shift_scale(_p(ints), C.c_int64(R), C.c_int64(d), C.c_int(bits), C.c_float(0.0),
+    L.launch_compute_row_shift_scale(_p(ints), C.c_int64(R), C.c_int64(d), C.c_int(bits), C.c_float(clip_k),
                                      _p(shifts), _p(scales), _stream())
     L.launch_apply_row_shift_clamp(_p(ints), C.c_int64(R), C.c_int64(d), _p(shifts), C.c_int(bits), _stream())
     L.launch_pack_bits_all_ballot_batch(_p(ints), C.c_int(R), C.c_longlong(d), C.c_int(bits), C.c_int(W),

@@ -8,7 +8,7 @@ from bsipytorch_b200 import capi
 _DT = {torch.float32: capi.DTYPE_F32, torch.float16: capi.DTYPE_F16, torch.bfloat16: capi.DTYPE_BF16}
 
 
-def quantize_pack(x, decimal_places=2, bits=7, chunk_mode=True, want_q8=True):
+def quantize_pack(x, decimal_places=2, bits=7, chunk_mode=True, want_q8=True, clip_k=0.0):
     assert x.is_cuda and x.dim() == 2
     x = x.contiguous()
     rows, D = x.shape
@@ -21,9 +21,15 @@ def quantize_pack(x, decimal_places=2, bits=7, chunk_mode=True, want_q8=True):
     shifts = torch.zeros(sshape, dtype=torch.int32, device=dev)
     ld8 = max(chunks, 1) * 256
     q8 = torch.full((rows, ld8), 99, dtype=torch.int8, device=dev) if want_q8 else None
-    rc = capi.lib().bsi_b200_quantize_pack(capi.ptr(x), _DT[x.dtype], rows, D, D, decimal_places, bits,
-                                           1 if chunk_mode else 0, capi.ptr(words), capi.ptr(scales),
-                                           capi.ptr(shifts), capi.ptr(q8), ld8, capi.stream_ptr())
+    if clip_k > 0.0:
+        rc = capi.lib().bsi_b200_quantize_pack_clip(capi.ptr(x), _DT[x.dtype], rows, D, D, decimal_places, bits,
+                                                    1 if chunk_mode else 0, C.c_float(clip_k), capi.ptr(words),
+                                                    capi.ptr(scales), capi.ptr(shifts), capi.ptr(q8), ld8,
+                                                    capi.stream_ptr())
+    else:
+        rc = capi.lib().bsi_b200_quantize_pack(capi.ptr(x), _DT[x.dtype], rows, D, D, decimal_places, bits,
+                                               1 if chunk_mode else 0, capi.ptr(words), capi.ptr(scales),
+                                               capi.ptr(shifts), capi.ptr(q8), ld8, capi.stream_ptr())
     capi.check(rc, "bsi_b200_quantize_pack")
     return dict(words=words, scales=scales, shifts=shifts, q8=q8)
 

@@ -5,11 +5,21 @@ import numpy as np
 import torch
 
 PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_fixed76.npz")
+MODES_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_modes.npz")
 DOT_CASES = ("c1", "fc1", "fc2")
 
 
 def load():
     return np.load(PATH)
+
+
+def load_modes():
+    """Variable-slice mode, row-scale dots and outlier clipping through the reference's kernels."""
+    return np.load(MODES_PATH)
+
+
+def f16(g, key):
+    return torch.from_numpy(g[key].copy()).view(torch.float16)
 
 
 def case_inputs(g, name):

@@ -7,7 +7,9 @@ Run on a machine with a GPU and ``oracle/_ref/ref_kernels.so`` (the reference's
 
 It writes ``ref_fixed76.npz``: seeded inputs plus what the reference kernels produced for them --
 packed query/key words, shifts and scales, clamped key integers, EWAH streams, and fixed76
-chunk-scale dot outputs. The CPU checker (``oracle/``) and the CUDA library are both tested
+chunk-scale dot outputs -- and ``ref_modes.npz`` with the other modes of the path: the variable-slice
+mode (int64 rounding + ballot packer, generic float-weight dot kernels), the fixed-bit row-scale dot
+(word counts that rule out chunk scales) and packing with outlier clipping. The CPU checker (``oracle/``) and the CUDA library are both tested
 against this file. Inputs are synthetic (shapes and value distributions of the benchmark
 configurations, scaled down); nothing here comes from an evaluation dataset.
 """
@@ -128,5 +130,79 @@ def main(outdir):
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")
 
 
+def bit_length(v):
+    return int(v).bit_length()
+
+
+def modes(outdir):
+    """Variable-slice mode, row-scale dot, outlier clipping: what the reference kernels give for them."""
+    assert ref_gpu.available(), "needs a GPU and oracle/_ref/ref_kernels.so"
+    dev = "cuda"
+    out = {}
+    si = np.float32(1.0 / 10.0 ** 4)
+
+    # variable-slice mode (bsi_vector_cuda.cpp:746-754): slice count = bit_width(max |v|) + 2, at least 2; queries
+    # per batch, keys here at the widest row's count (a narrower row sign-extends to it)
+    q, k = _inputs.c1(Q=32, R=64, D=512)
+    k = k.half().float()
+    qd, kd = q.to(dev), k.to(dev)
+    _, qi = ref_gpu.pack_plain(qd, 2, 2)
+    _, ki = ref_gpu.pack_plain(kd, 2, 2)
+    Sq = max(2, bit_length(qi.abs().max().item()) + 2)
+    Sk = max(2, bit_length(ki.abs().max().item()) + 2)
+    qw, _ = ref_gpu.pack_plain(qd, 2, Sq)
+    kw, _ = ref_gpu.pack_plain(kd, 2, Sk)
+    Aw = ref_gpu.slice_weights(Sq, 32, dev)
+    Bw = ref_gpu.slice_weights(Sk, 64, dev)
+    out["var_q"] = q.numpy()
+    out["var_k_f16bits"] = k.half().view(torch.int16).numpy()
+    out["var_q_ints"] = qi.cpu().numpy().astype(np.int32)
+    out["var_k_ints"] = ki.cpu().numpy().astype(np.int32)
+    out["var_q_words"] = u64(qw)
+    out["var_k_words"] = u64(kw)
+    out["var_out_tc"] = ref_gpu.dot_generic(qw, Aw, kw, Bw, si, tensor_core=True).cpu().numpy()
+    out["var_out_plain"] = ref_gpu.dot_generic(qw, Aw, kw, Bw, si, tensor_core=False).cpu().numpy()
+
+    # fixed-bit mode with one scale per query row: BSI_FIXED_CHUNK_SCALE=0 ("row", 8 words per slice, tensor-core
+    # and plain generic kernels) and a word count that rules chunk scales out ("rowr", 5 words per slice:
+    # bsi_vector_cuda.cpp:980-994; the dispatcher then takes the plain kernel whatever the switch says)
+    for tag, D in (("row", 512), ("rowr", 320)):
+        q, k = _inputs.fc1(Q=32, R=32, D=D, dtype=torch.float32)
+        k = k.half().float()
+        qd, kd = q.to(dev), k.to(dev)
+        qw, qsh, qsc, qint = ref_gpu.pack_rows(qd, 2, 7)
+        kw, ksh, ksc, kint = ref_gpu.pack_rows(kd, 2, 6)
+        Aw = ref_gpu.slice_weights(7, 32, dev, qsc)
+        Bw = ref_gpu.slice_weights(6, 32, dev, ksc)
+        out[f"{tag}_q"] = q.numpy()
+        out[f"{tag}_k_f16bits"] = k.half().view(torch.int16).numpy()
+        out[f"{tag}_q_words"] = u64(qw)
+        out[f"{tag}_q_scales"] = qsc.cpu().numpy()
+        out[f"{tag}_k_words"] = u64(kw)
+        out[f"{tag}_k_scales"] = ksc.cpu().numpy()
+        out[f"{tag}_out_tc"] = ref_gpu.dot_generic(qw, Aw, kw, Bw, si, tensor_core=True).cpu().numpy()
+        out[f"{tag}_out_plain"] = ref_gpu.dot_generic(qw, Aw, kw, Bw, si, tensor_core=False).cpu().numpy()
+
+    # outlier clipping (BSI_FIXED_CLIP_K = 3)
+    x, kx = _inputs.fc1(Q=16, R=16, D=1000, dtype=torch.float16)
+    w, sh, sc = ref_gpu.pack_queries_chunk(x.to(dev), 2, 7, clip_k=3.0)
+    out["clip_x_f16bits"] = x.view(torch.int16).numpy()
+    out["clip_words"] = u64(w)
+    out["clip_shifts"] = sh.cpu().numpy()
+    kx = kx.half().float()
+    kw, ksh, ksc, kint = ref_gpu.pack_rows(kx.to(dev), 2, 6, clip_k=3.0)
+    out["clip_k_f16bits"] = kx.half().view(torch.int16).numpy()
+    out["clip_row_words"] = u64(kw)
+    out["clip_row_shifts"] = ksh.cpu().numpy()
+    out["clip_row_ints"] = kint.cpu().numpy().astype(np.int8)
+    torch.cuda.synchronize()
+    os.makedirs(outdir, exist_ok=True)
+    path = os.path.join(outdir, "ref_modes.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")
+
+
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else HERE)
+    target = sys.argv[1] if len(sys.argv) > 1 else HERE
+    main(target)
+    modes(target)

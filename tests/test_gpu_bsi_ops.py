@@ -262,3 +262,28 @@ def test_keyset_save_load_round_trip(bsi_ops, tmp_path):
     open(bad, "wb").write(bytes(raw[:100]))
     with pytest.raises(RuntimeError):
         bsi_ops.load_keyset(bad)
+
+
+def test_outlier_clipping_env(bsi_ops, monkeypatch):
+    """BSI_FIXED_CLIP_K > 0 (bsi_vector_cuda.cpp:295-307): builders and dots follow the checker's clipped shifts; the
+    fused additions, which have no clipping variant, refuse to run."""
+    monkeypatch.setenv("BSI_FIXED_CLIP_K", "3.0")
+    q, k = _inputs.fc1(Q=40, R=96, D=1024)
+    keys_cap, *_ = bsi_ops.build_bsi_keys_cuda(k, 2, 0.5)
+    qcap = bsi_ops.build_bsi_queries_cuda_batch_packed(q.to(DEV), 2, 0.5)
+    qt = bsi_ops.debug_query_batch_tensors(qcap)
+    qa = o.quantize_pack(q.float().numpy(), 2, 7, True, 3.0)
+    np.testing.assert_array_equal(H.as_u64(qt["words"]), qa["words"])
+    np.testing.assert_array_equal(qt["scales"].cpu().numpy(), qa["scales"])
+    assert not np.array_equal(qa["scales"], o.quantize_pack(q.float().numpy(), 2, 7, True)["scales"])
+    out, *_ = bsi_ops.batch_dot_product_multiquery_cuda_batch_caps(qcap, keys_cap)
+    want = o.fixed_dot(q.float().numpy(), k.numpy(), clip_k=3.0)
+    np.testing.assert_array_equal(_bits(out), want.view(np.uint32))
+    out_l, *_ = bsi_ops.batch_dot_product_multiquery_cuda_caps(bsi_ops.build_bsi_queries_cuda_batch(q.to(DEV), 2, 0.5), keys_cap)
+    assert torch.equal(out_l, out)
+    y = bsi_ops.bsi_linear_forward(q.to(DEV), keys_cap, None, 2)          # packs through the same builder
+    assert torch.equal(y, out.to(y.dtype))
+    q8 = torch.empty(40, 1024, dtype=torch.int8, device=DEV)
+    sc = torch.empty(40, 4, dtype=torch.float32, device=DEV)
+    with pytest.raises(RuntimeError, match="BSI_FIXED_CLIP_K"):
+        bsi_ops.pack_queries_into(q.to(DEV), q8, sc, 2)

@@ -12,9 +12,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def _check(x_cpu, bits, chunk_mode, dp=2):
-    got = H.quantize_pack(x_cpu.to(DEV), dp, bits, chunk_mode)
-    want = o.quantize_pack(x_cpu.float().numpy(), dp, bits, chunk_mode)
+def _check(x_cpu, bits, chunk_mode, dp=2, clip_k=0.0):
+    got = H.quantize_pack(x_cpu.to(DEV), dp, bits, chunk_mode, clip_k=clip_k)
+    want = o.quantize_pack(x_cpu.float().numpy(), dp, bits, chunk_mode, clip_k)
     D = x_cpu.shape[1]
     np.testing.assert_array_equal(got["shifts"].cpu().numpy(), want["shifts"])
     np.testing.assert_array_equal(got["scales"].cpu().numpy(), want["scales"])
@@ -147,3 +147,28 @@ def test_pack_matches_reference_kernels():
     mine = H.quantize_pack(edge, 2, 7, True)
     words, shifts, scales = ref_gpu.pack_queries_chunk(edge, 2, 7)
     assert torch.equal(mine["words"], words) and torch.equal(mine["shifts"], shifts)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("clip_k", [1.5, 3.0, 50.0])
+def test_pack_with_outlier_clipping(dtype, clip_k):
+    """BSI_FIXED_CLIP_K of the reference: the shift of a chunk / row follows min(max |v|, clip_k * mean |v|); outliers
+    saturate. Against the checker, and against the reference's own kernels where they were built."""
+    g = torch.Generator().manual_seed(int(clip_k * 10))
+    x = torch.randn(37, 1000, generator=g) * torch.where(torch.rand(37, 1000, generator=g) < 0.02, 30.0, 1.0)
+    x[3] = 0.0
+    x[4, 10] = 1.0e4
+    x = x.to(dtype)
+    got_c = _check(x, 7, True, clip_k=clip_k)
+    got_r = _check(x * 0.02, 6, False, clip_k=clip_k)
+    plain = H.quantize_pack(x.to(DEV), 2, 7, True)
+    if clip_k < 10:
+        assert not torch.equal(plain["shifts"], got_c["shifts"]), "clipping must change some shifts on this input"
+        assert int(got_c["q8"].max()) == 63 and int(got_c["q8"].min()) == -64     # saturated outliers
+    from oracle import ref_gpu
+    if ref_gpu.available():
+        words, shifts, scales = ref_gpu.pack_queries_chunk(x.to(DEV), 2, 7, clip_k=clip_k)
+        assert torch.equal(got_c["words"], words) and torch.equal(got_c["shifts"], shifts) and torch.equal(got_c["scales"], scales)
+        words, shifts, scales, ints = ref_gpu.pack_rows((x * 0.02).to(DEV), 2, 6, clip_k=clip_k)
+        assert torch.equal(got_r["words"], words) and torch.equal(got_r["shifts"], shifts)
+        assert torch.equal(got_r["q8"][:, :1000].long(), ints)

@@ -85,3 +85,47 @@ def test_ewah_structured(g, W, thr):
     np.testing.assert_array_equal(length, g[f"{tag}_len"])
     for s in range(words.shape[0]):
         np.testing.assert_array_equal(o.ewah_decode(stream[off[s]: off[s] + length[s]], W), words[s])
+
+
+@pytest.fixture(scope="module")
+def m():
+    return _golden.load_modes()
+
+
+def test_variable_slice_mode_against_reference_kernels(m):
+    q, k = m["var_q"], _golden.f16(m, "var_k_f16bits").float().numpy()
+    qa, kb = o.variable_pack(q, 2), o.variable_pack(k, 2, per_row=True)
+    np.testing.assert_array_equal(qa["ints"], m["var_q_ints"])
+    np.testing.assert_array_equal(kb["ints"], m["var_k_ints"])
+    np.testing.assert_array_equal(qa["words"], m["var_q_words"])
+    np.testing.assert_array_equal(kb["words"], m["var_k_words"])
+    want = o.variable_dot(q, k, 2).view(np.uint32)
+    np.testing.assert_array_equal(want, m["var_out_tc"].view(np.uint32))
+    np.testing.assert_array_equal(want, m["var_out_plain"].view(np.uint32))
+
+
+@pytest.mark.parametrize("tag", ["row", "rowr"])
+def test_row_scale_dot_against_reference_kernels(m, tag):
+    q, k = m[f"{tag}_q"], _golden.f16(m, f"{tag}_k_f16bits").float().numpy()
+    qa = o.quantize_pack(q, 2, 7, False)
+    kb = o.quantize_pack(k, 2, 6, False)
+    np.testing.assert_array_equal(qa["words"], m[f"{tag}_q_words"])
+    np.testing.assert_array_equal(qa["scales"], m[f"{tag}_q_scales"])
+    np.testing.assert_array_equal(kb["words"], m[f"{tag}_k_words"])
+    np.testing.assert_array_equal(kb["scales"], m[f"{tag}_k_scales"])
+    got = o.fixed_dot(q, k, 2, chunk_scale=False).view(np.uint32)
+    np.testing.assert_array_equal(got, m[f"{tag}_out_tc"].view(np.uint32))
+    np.testing.assert_array_equal(got, m[f"{tag}_out_plain"].view(np.uint32))
+
+
+def test_outlier_clipping_against_reference_kernels(m):
+    x = _golden.f16(m, "clip_x_f16bits").float().numpy()
+    qa = o.quantize_pack(x, 2, 7, True, 3.0)
+    np.testing.assert_array_equal(qa["words"], m["clip_words"])
+    np.testing.assert_array_equal(qa["shifts"], m["clip_shifts"])
+    k = _golden.f16(m, "clip_k_f16bits").float().numpy()
+    kb = o.quantize_pack(k, 2, 6, False, 3.0)
+    np.testing.assert_array_equal(kb["words"], m["clip_row_words"])
+    np.testing.assert_array_equal(kb["shifts"], m["clip_row_shifts"])
+    np.testing.assert_array_equal(kb["qvals"], m["clip_row_ints"])
+    assert not np.array_equal(qa["shifts"], o.quantize_pack(x, 2, 7, True)["shifts"])
