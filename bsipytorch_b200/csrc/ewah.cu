@@ -187,9 +187,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_kernel(
 // kScanItems consecutive sizes per tile (all of its loads are in flight together, and the next tile's are
 // issued before the current tile is scanned), so a tile of 8192 slices costs one round of block barriers.
 constexpr int kScanItems = 8;
-__global__ void __launch_bounds__(1024) ewah_offsets_kernel(const u64* __restrict__ sizes, int64_t S,
-                                                            u64* __restrict__ off,
-                                                            u64* __restrict__ total) {
+__device__ __forceinline__ void exclusive_scan_block(const u64* __restrict__ sizes, int64_t S,
+                                                     u64* __restrict__ off, u64* __restrict__ total) {
     __shared__ u64 warp_tot[32];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -238,6 +237,22 @@ __global__ void __launch_bounds__(1024) ewah_offsets_kernel(const u64* __restric
         for (int k = 0; k < kScanItems; ++k) v[k] = nxt[k];
     }
     if (threadIdx.x == 0 && total != nullptr) *total = carry;
+}
+
+__global__ void __launch_bounds__(1024) ewah_offsets_kernel(const u64* __restrict__ sizes, int64_t S,
+                                                            u64* __restrict__ off,
+                                                            u64* __restrict__ total) {
+    exclusive_scan_block(sizes, S, off, total);
+}
+
+// The same scan as the middle kernel of the one-call encoder, launched as a programmatic dependent of the sizes
+// pass: it lets the emit pass start (whose blocks first load their slices, which depend on nothing), then waits
+// for the sizes pass to be complete.
+__global__ void __launch_bounds__(1024) ewah_block_offsets_kernel(const u64* __restrict__ sums, int64_t n,
+                                                                  u64* __restrict__ off, u64* __restrict__ total) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    exclusive_scan_block(sums, n, off, total);
 }
 
 // Decode: lane 0 parses the RLWs in order (bsi_cuda_kernels_ewah.cuh:16-32), the warp fills runs
@@ -423,6 +438,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_sizes_kernel(
     const u64* __restrict__ words, int64_t S, int64_t W, double threshold, const FlagCuts cuts,
     int32_t* __restrict__ flags, u64* __restrict__ sizes, u64* __restrict__ block_sums) {
     __shared__ u64 wsize[kWarpsPerBlock];
+    // the scan and the emit pass are launched as programmatic dependents: once every block of this grid runs,
+    // theirs may be scheduled into SMs that fall idle (they wait for this grid's results where they need them)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int64_t s = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock + warp;
@@ -468,6 +486,13 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_blocks_kernel(
     const int warp = threadIdx.x >> 5;
     const int64_t s0 = static_cast<int64_t>(blockIdx.x) * kWarpsPerBlock;
     const int64_t s = s0 + warp;
+    // The slice itself is input of the whole call: it is loaded before the wait for the two passes before this one
+    // (programmatic dependent launch), so that this read overlaps their tail and the scan.
+    u64 wv[TILES > 0 ? TILES : 1];
+    if constexpr (TILES > 0) {
+        if (s < S) load_slice<TILES>(words + s * W, W, lane, wv);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     // every warp adds up the sizes of the block's slices before its own
     u64 mine = (lane < kWarpsPerBlock && s0 + lane < S) ? sizes[s0 + lane] : 0ull;
     u64 before = (lane < warp) ? mine : 0ull;
@@ -480,16 +505,29 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_blocks_kernel(
         if (lane == 0) out_len[s] = static_cast<int32_t>(n_expected);
         return;
     }
-    const u64* base = words + s * W;
     u64 n;
     if constexpr (TILES > 0) {
-        u64 wv[TILES];
-        load_slice<TILES>(base, W, lane, wv);
         n = encode_slice_regs<true, TILES>(wv, W, flags[s], out + o, lane);
     } else {
-        n = encode_slice<true>(base, W, flags[s], out + o, lane);
+        n = encode_slice<true>(words + s * W, W, flags[s], out + o, lane);
     }
     if (lane == 0) out_len[s] = static_cast<int32_t>(n);
+}
+
+// Launch as a programmatic dependent of the kernel before it in the stream: the kernel may start while that one
+// drains and must execute griddepcontrol.wait before it reads what earlier kernels of the stream wrote.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 inline unsigned warp_blocks(int64_t S) { return static_cast<unsigned>((S + kWarpsPerBlock - 1) / kWarpsPerBlock); }
@@ -653,11 +691,13 @@ extern "C" int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W,
     else BSI_EWAH_SIZES(0);
 #undef BSI_EWAH_SIZES
     if (int rc = check_launch("ewah_encode sizes launch")) return rc;
-    ewah_offsets_kernel<<<1, 1024, 0, stream>>>(block_sums, nb, block_off, reinterpret_cast<u64*>(total));
+    BSI_CUDA_TRY(launch_dependent(ewah_block_offsets_kernel, 1u, 1024u, stream, static_cast<const u64*>(block_sums), nb,
+                                  block_off, reinterpret_cast<u64*>(total)));
     if (int rc = check_launch("ewah_encode offsets launch")) return rc;
-#define BSI_EWAH_EMIT(T) ewah_emit_blocks_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                     \
-        w64, S, W, flags, sizes, block_off, static_cast<u64>(capacity), reinterpret_cast<u64*>(off),                \
-        reinterpret_cast<u64*>(out), out_len)
+#define BSI_EWAH_EMIT(T) BSI_CUDA_TRY(launch_dependent(ewah_emit_blocks_kernel<T>, grid, kWarpsPerBlock * 32u, stream, \
+        w64, S, W, static_cast<const int32_t*>(flags), static_cast<const u64*>(sizes),                                \
+        static_cast<const u64*>(block_off), static_cast<u64>(capacity), reinterpret_cast<u64*>(off),                  \
+        reinterpret_cast<u64*>(out), out_len))
     if (W <= 32) BSI_EWAH_EMIT(1);
     else if (W <= 64) BSI_EWAH_EMIT(2);
     else if (W <= 128) BSI_EWAH_EMIT(4);
