@@ -124,6 +124,19 @@ __device__ __forceinline__ u64 transpose8x8(u64 x) {
     return x;
 }
 
+// The same transposition on the two 32-bit halves (lo = rows 0..3, hi = rows 4..7): the first two exchange steps
+// stay inside a half, the third swaps the high nibbles of lo with the low nibbles of hi.
+__device__ __forceinline__ void transpose8x8_halves(uint32_t& lo, uint32_t& hi) {
+    uint32_t t;
+    t = (lo ^ (lo >> 7)) & 0x00AA00AAu;  lo = lo ^ t ^ (t << 7);
+    t = (hi ^ (hi >> 7)) & 0x00AA00AAu;  hi = hi ^ t ^ (t << 7);
+    t = (lo ^ (lo >> 14)) & 0x0000CCCCu; lo = lo ^ t ^ (t << 14);
+    t = (hi ^ (hi >> 14)) & 0x0000CCCCu; hi = hi ^ t ^ (t << 14);
+    t = (lo ^ (hi << 4)) & 0xF0F0F0F0u;
+    lo ^= t;
+    hi ^= t >> 4;
+}
+
 // Loads the 8 elements [col, col+8) of a row as float; elements at or beyond D read as 0.
 template <typename T>
 __device__ __forceinline__ void load8(const T* __restrict__ row, int64_t col, int64_t D, bool vec_ok,
@@ -314,16 +327,28 @@ __device__ __forceinline__ bool fast_chunk(const float (&f)[8], uint32_t unit, u
     }
     if constexpr (kQ8) *reinterpret_cast<u64*>(q8 + q8_off) = packed;
     if constexpr (kWords) {
+        // After the 8x8 bit transposition a lane holds one byte of each slice. Four neighbouring lanes (half a
+        // 64-bit word) trade bytes in two shuffle steps so that each ends up with the four bytes of two slices:
+        // two 4-byte stores per lane instead of seven 1-byte stores.
+        uint32_t tl = static_cast<uint32_t>(packed), th = static_cast<uint32_t>(packed >> 32);
+        transpose8x8_halves(tl, th);
+        const bool upper = (lane & 2) != 0;     // lanes 2, 3 of the group collect slices 4..7, lanes 0, 1 slices 0..3
+        const bool odd = (lane & 1) != 0;       // odd lanes keep the second slice pair of their group
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, upper ? tl : th, 2);
+        const uint32_t x = upper ? got : tl;    // the slice group's bytes of group lane (lane & 1)
+        const uint32_t y = upper ? th : got;    // ... and of group lane (lane & 1) + 2
+        const uint32_t keep = __byte_perm(x, y, odd ? 0x7632 : 0x5410);
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, __byte_perm(x, y, odd ? 0x5410 : 0x7632), 1);
+        const uint32_t w0 = __byte_perm(keep, other, odd ? 0x2604 : 0x6240);   // bytes of group lanes 0, 1, 2, 3
+        const uint32_t w1 = __byte_perm(keep, other, odd ? 0x3715 : 0x7351);
         if (word_ok) {
-            const u64 t = transpose8x8(packed);
-            const uint32_t tl = static_cast<uint32_t>(t), th = static_cast<uint32_t>(t >> 32);
+            const int s0 = ((lane & 2) << 1) + ((lane & 1) << 1);              // first of the lane's two slices
             uint8_t* out = reinterpret_cast<uint8_t*>(words);
-            uint32_t off = word_off;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                if (s < bits) out[off] = static_cast<uint8_t>((s < 4 ? tl : th) >> (8 * (s & 3)));
-                off += slice_bytes;
-            }
+            // word_off addresses the lane's own byte (word lane / 8, byte lane % 8); the 4-byte store goes to
+            // the start of its half word
+            const uint32_t off = word_off - (lane & 3) + static_cast<uint32_t>(s0) * slice_bytes;
+            if (s0 < bits) *reinterpret_cast<uint32_t*>(out + off) = w0;
+            if (s0 + 1 < bits) *reinterpret_cast<uint32_t*>(out + off + slice_bytes) = w1;
         }
     }
     return true;
