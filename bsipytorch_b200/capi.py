@@ -28,6 +28,9 @@ SIGNATURES = {
     "bsi_b200_quantize_pack_clip": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _i64, _vp]),
     "bsi_b200_decimal_absmax": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _vp, _vp]),
     "bsi_b200_pack_plain": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "bsi_b200_register_key_bounds": (_i32, [_vp, _vp, _i64, _i32]),
+    "bsi_b200_unregister_key_bounds": (_i32, [_vp]),
+    "bsi_b200_debug_exact_int_tiles": (_i32, [_vp]),
     "bsi_b200_recombine_i8": (_i32, [_vp, _i64, _i32, _i64, _vp, _i64, _vp]),
     "bsi_b200_dot_i8": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _vp, _i32, _vp]),
     "bsi_b200_linear_i8": (_i32, [_vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _vp, _i64, _i32, _vp]),
@@ -92,6 +95,13 @@ def ptr(t):
 def stream_ptr():
     import torch
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def exact_int_tiles() -> int:
+    """(warp, tile) pairs of the paired tensor-core kernel that took the integer route since the last call."""
+    v = C.c_ulonglong(0)
+    check(lib().bsi_b200_debug_exact_int_tiles(C.byref(v)), "bsi_b200_debug_exact_int_tiles")
+    return v.value
 
 
 def device_status() -> int:

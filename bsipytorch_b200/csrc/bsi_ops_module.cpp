@@ -129,6 +129,24 @@ struct PrebuiltBSIKeysCUDA {
     PackedBatch b;
     int64_t num_keys = 0;
     float threshold = 0.2f;
+    at::Tensor abs_sum;      // [2, num_keys] float32: sum of |k| over each row of the int8 image, then the largest
+                             // such sum over one 256-element chunk of the row (integers below 2^24: exact)
+    ~PrebuiltBSIKeysCUDA() {
+        if (abs_sum.defined() && b.q8.defined()) bsi_b200_unregister_key_bounds(b.q8.data_ptr<int8_t>());
+    }
+    // Row sums of |k| for the exact-integer route of the tensor-core dots (bsi_b200_register_key_bounds).
+    void compute_bounds() {
+        if (!b.q8.defined() || b.q8.numel() == 0 || b.variable) return;
+        c10::cuda::CUDAGuard guard(b.q8.device());
+        at::Tensor per_chunk = b.q8.to(at::kInt).abs_().view({b.q8.size(0), -1, 256}).sum(2);   // [R, chunks]
+        abs_sum = at::stack({per_chunk.sum(1), per_chunk.amax(1)}, 0).to(at::kFloat).contiguous();
+    }
+    // Called before every dot on these keys: the bound depends on the width of the queries of that dot.
+    void register_bounds(int query_bits) const {
+        if (!abs_sum.defined()) return;
+        const int qmax = (query_bits >= 2 && query_bits <= 8) ? (1 << (query_bits - 1)) : 128;
+        bsi_b200_register_key_bounds(b.q8.data_ptr<int8_t>(), abs_sum.data_ptr<float>(), num_keys, qmax);
+    }
 };
 
 struct PrebuiltBSIQueryBatchCUDA {
@@ -344,6 +362,7 @@ py::tuple build_bsi_keys_cuda(torch::Tensor K, int decimalPlaces, float compress
                            : pack(K, decimalPlaces, kbits, /*chunk_mode=*/false, /*profile=*/false);
     holder->num_keys = K.size(0);
     holder->threshold = compress_threshold;
+    holder->compute_bounds();
     uint64_t total_mem_bytes = static_cast<uint64_t>(holder->b.words.numel() * holder->b.words.element_size());
     if (holder->b.variable) {   // what the reference's per-row vectors would hold: each row its own slice count
         total_mem_bytes = 0;
@@ -501,6 +520,7 @@ py::tuple run_dot(const PackedBatch& qb, const PrebuiltBSIKeysCUDA& keys, bool w
     }
     const int engine = engine_from_env();
     const int64_t qs_stride = qb.chunk_mode ? qb.chunks : 0;
+    keys.register_bounds(qb.variable ? 8 : qb.S);
     if (qb.variable || keys.b.variable) {
         TORCH_CHECK(engine != BSI_ENGINE_BMMA, "the b1 mma.sync engine reads fixed-bit slices; variable-slice operands use the int8 engines");
         TORCH_CHECK(!want_iacc, "the per-chunk accumulator dump is defined for the fixed-bit mode");
@@ -684,6 +704,7 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
     }
     const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
     if (fused) {
+        keys->register_bounds(qb.S);
         check_status(bsi_b200_linear_i8(qb.q8.data_ptr<int8_t>(), qb.q8.size(1), qb.scales.data_ptr<float>(),
                                         qb.chunk_mode ? qb.chunks : 0, keys->b.q8.data_ptr<int8_t>(),
                                         keys->b.q8.size(1), keys->b.scales.data_ptr<float>(), bptr, Q, R, qb.chunks,
@@ -759,6 +780,7 @@ at::Tensor linear_from_packed(torch::Tensor q8, torch::Tensor scales, py::capsul
         bptr = b32.data_ptr<float>();
     }
     const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
+    keys->register_bounds(bits_queries());
     check_status(bsi_b200_linear_i8_act(q8.data_ptr<int8_t>(), q8.stride(0), scales.data_ptr<float>(), chunks,
                                         keys->b.q8.data_ptr<int8_t>(), keys->b.q8.size(1), keys->b.scales.data_ptr<float>(),
                                         bptr, Q, R, chunks, static_cast<float>(scale_inv), y.data_ptr(), R, code,
@@ -852,6 +874,7 @@ void linear_from_packed_scatter(torch::Tensor q8, torch::Tensor scales, py::caps
     std::vector<void*> y;
     for (int64_t p : y_ptrs) y.push_back(reinterpret_cast<void*>(static_cast<intptr_t>(p)));
     const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
+    keys->register_bounds(bits_queries());
     check_status(bsi_b200_linear_i8_scatter(q8.data_ptr<int8_t>(), q8.stride(0), scales.data_ptr<float>(), chunks,
                                             keys->b.q8.data_ptr<int8_t>(), keys->b.q8.size(1),
                                             keys->b.scales.data_ptr<float>(), bptr, Q, R, chunks,
@@ -896,6 +919,7 @@ void linear_from_packed_requant(torch::Tensor q8, torch::Tensor scales, py::caps
     std::vector<float*> sd;
     for (int64_t p : q8_ptrs) qd.push_back(reinterpret_cast<int8_t*>(static_cast<intptr_t>(p)));
     for (int64_t p : scale_ptrs) sd.push_back(reinterpret_cast<float*>(static_cast<intptr_t>(p)));
+    keys->register_bounds(bits_queries());
     check_status(bsi_b200_linear_i8_requant(q8.data_ptr<int8_t>(), q8.stride(0), scales.data_ptr<float>(), chunks,
                                             keys->b.q8.data_ptr<int8_t>(), keys->b.q8.size(1),
                                             keys->b.scales.data_ptr<float>(), bptr, Q, R, chunks,
@@ -959,7 +983,10 @@ py::dict debug_query_batch_tensors(py::capsule cap) {
     return debug_batch(from_capsule<PrebuiltBSIQueryBatchCUDA>(cap, "PrebuiltBSIQueryBatchCUDA")->b);
 }
 py::dict debug_keys_tensors(py::capsule cap) {
-    return debug_batch(from_capsule<PrebuiltBSIKeysCUDA>(cap, "PrebuiltBSIKeysCUDA")->b);
+    auto* keys = from_capsule<PrebuiltBSIKeysCUDA>(cap, "PrebuiltBSIKeysCUDA");
+    py::dict d = debug_batch(keys->b);
+    if (keys->abs_sum.defined()) d["abs_sum"] = keys->abs_sum;   // [2, R]: what register_key_bounds is given
+    return d;
 }
 py::dict debug_query_tensors(py::capsule cap) {
     auto* q = from_capsule<PrebuiltBSIQueryCUDA>(cap, "PrebuiltBSIQueryCUDA");
@@ -1166,6 +1193,7 @@ py::tuple load_keyset(const std::string& dir_or_file) {
     }
     holder->num_keys = R;
     holder->threshold = h.threshold;
+    holder->compute_bounds();
     const uint64_t total_mem_bytes = static_cast<uint64_t>(b.words.numel() * b.words.element_size());
     py::capsule cap(holder, "PrebuiltBSIKeysCUDA", [](PyObject* c) {
         delete reinterpret_cast<PrebuiltBSIKeysCUDA*>(PyCapsule_GetPointer(c, "PrebuiltBSIKeysCUDA"));

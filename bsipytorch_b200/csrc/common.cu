@@ -5,6 +5,9 @@
 
 #include <stdarg.h>
 
+#include <mutex>
+#include <unordered_map>
+
 namespace bsi {
 
 static thread_local char g_err[512] = "";
@@ -23,6 +26,21 @@ bool pdl_enabled() {
         cached = (e != nullptr && e[0] == '0') ? 0 : 1;
     }
     return cached == 1;
+}
+
+namespace {
+std::mutex g_bounds_mu;
+std::unordered_map<const void*, KeyBounds> g_bounds;
+}  // namespace
+
+bool lookup_key_bounds(const void* k8, KeyBounds* out) {
+    const char* e = getenv("BSI_B200_EXACT_INT");      // 0 switches the integer accumulation off (A/B comparisons)
+    if (e != nullptr && e[0] == '0') return false;
+    std::lock_guard<std::mutex> lock(g_bounds_mu);
+    auto it = g_bounds.find(k8);
+    if (it == g_bounds.end()) return false;
+    *out = it->second;
+    return true;
 }
 
 int sm_count() {
@@ -79,3 +97,21 @@ extern "C" const char* bsi_b200_status_string(int status) {
 extern "C" const char* bsi_b200_last_error(void) { return bsi::g_err; }
 
 extern "C" int bsi_b200_version(void) { return BSI_B200_VERSION; }
+
+extern "C" int bsi_b200_register_key_bounds(const int8_t* k8, const float* key_abs_sum, int64_t R, int query_abs_max) {
+    using namespace bsi;
+    if (k8 == nullptr || key_abs_sum == nullptr || R <= 0 || query_abs_max <= 0 || query_abs_max > 128) {
+        set_error("register_key_bounds: bad argument");
+        return BSI_ERR_INVALID;
+    }
+    std::lock_guard<std::mutex> lock(g_bounds_mu);
+    g_bounds[k8] = KeyBounds{key_abs_sum, R, static_cast<float>(query_abs_max)};
+    return BSI_OK;
+}
+
+extern "C" int bsi_b200_unregister_key_bounds(const int8_t* k8) {
+    using namespace bsi;
+    std::lock_guard<std::mutex> lock(g_bounds_mu);
+    g_bounds.erase(k8);
+    return BSI_OK;
+}

@@ -35,6 +35,8 @@ namespace bsi {
 
 // Device-side status word: 0 = clean; otherwise the site code of the first wait that gave up.
 __device__ int g_device_status = 0;
+// warp-tiles of the paired kernel that took the integer accumulation (a test hook: bsi_b200_debug_exact_int_tiles)
+__device__ unsigned long long g_exact_int_tiles = 0ull;
 
 namespace {
 
@@ -445,7 +447,7 @@ template <int BN, bool DBG, typename OutT, bool REQ = false>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
                 const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
                 float scale_inv, void* out, int64_t ldo, int32_t* dbg, const ScatterDst& scatter,
-                const RequantDst& requant, cudaStream_t stream) {
+                const RequantDst& requant, const float* k_abs_sum, float q_abs_max, cudaStream_t stream) {
     using C = pair::Cfg<BN>;
     static int max_clusters[64] = {0};   // per instantiation
     int dev = 0;
@@ -480,7 +482,8 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     int pairs = tiles_total < resident ? tiles_total : resident;
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT, REQ>, ma, mb, vector_store, qs,
-                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter, requant));
+                                    qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter, requant,
+                                    k_abs_sum, q_abs_max));
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
@@ -569,9 +572,17 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
         (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo % per16) == 0 && (R % per16) == 0) ? 1 : 0) |
         (relu ? 2 : 0);   // the kernel's store_flags
     const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
+    // bounds registered for this key image switch on the integer accumulation where it is provably exact
+    KeyBounds kb = {};
+    const float* kabs = nullptr;
+    float qabs = 0.0f;
+    if (lookup_key_bounds(k8, &kb) && kb.rows == R) {
+        kabs = kb.abs_sum;
+        qabs = kb.query_abs_max;
+    }
 #define BSI_PAIR_T(BN_, DBG_, T_)                                                                              \
     launch_pair<BN_, DBG_, T_>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv, out, ldo,  \
-                               dbg_iacc, scatter, requant, stream)
+                               dbg_iacc, scatter, requant, kabs, qabs, stream)
 #define BSI_PAIR(BN_)                                                                   \
     (y_dtype == BSI_DTYPE_F16    ? BSI_PAIR_T(BN_, false, __half)                       \
      : y_dtype == BSI_DTYPE_BF16 ? BSI_PAIR_T(BN_, false, __nv_bfloat16)                \
@@ -580,9 +591,9 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     if (requant.n > 0) {
         if (y_dtype == BSI_DTYPE_F16)
             return launch_pair<256, false, __half, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv,
-                                                         out, ldo, nullptr, scatter, requant, stream);
+                                                         out, ldo, nullptr, scatter, requant, kabs, qabs, stream);
         return launch_pair<256, false, __nv_bfloat16, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c,
-                                                            scale_inv, out, ldo, nullptr, scatter, requant, stream);
+                                                            scale_inv, out, ldo, nullptr, scatter, requant, kabs, qabs, stream);
     }
 #define BSI_PAIR_F32(BN_) (dbg_iacc ? BSI_PAIR_T(BN_, true, float) : BSI_PAIR_T(BN_, false, float))
     switch (bn) {
@@ -645,5 +656,17 @@ extern "C" int bsi_b200_device_status(int* status_out) {
     if (int rc = take_peer_status(&pv)) return rc;
     if (v == 0) v = pv;
     *status_out = v;
+    return BSI_OK;
+}
+
+extern "C" int bsi_b200_debug_exact_int_tiles(unsigned long long* count_out) {
+    using namespace bsi;
+    if (count_out == nullptr) return fail(BSI_ERR_INVALID, "debug_exact_int_tiles: null pointer");
+    BSI_CUDA_TRY(cudaDeviceSynchronize());
+    unsigned long long v = 0;
+    BSI_CUDA_TRY(cudaMemcpyFromSymbol(&v, g_exact_int_tiles, sizeof(v)));
+    const unsigned long long zero = 0;
+    BSI_CUDA_TRY(cudaMemcpyToSymbol(g_exact_int_tiles, &zero, sizeof(zero)));
+    *count_out = v;
     return BSI_OK;
 }

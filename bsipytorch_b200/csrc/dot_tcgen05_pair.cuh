@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const float* __restrict__ qs, int64_t qs_stride, const float* __restrict__ bw0,
     const float* __restrict__ bias, int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
     void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc, const ScatterDst scatter,
-    const RequantDst requant) {
+    const RequantDst requant, const float* __restrict__ k_abs_sum, float q_abs_max) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     constexpr int kCols = BN / 2;              // accumulator columns per epilogue warp: a multiple of 16
@@ -403,10 +403,81 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 }
             }
 
+            // Integer accumulation where it provably equals the float32 chain: the chunk terms I_c * 2^shift are
+            // integers, so while every prefix sum stays below 2^24 in magnitude no float32 addition rounds and
+            // acc += I_c << shift in int32 gives the same bits. With A the largest query magnitude, a prefix is at
+            // most A x (largest 2^shift of the row) x (sum of |k| over the key row), and also at most
+            // A x (sum of the row's 2^shift) x (largest sum of |k| over one chunk of the key row); the key sums come
+            // from the caller (k_abs_sum: R row sums, then R chunk maxima; null: not available). The test is made
+            // for the warp's 32 rows x kCols columns at once, so the branch is uniform; a warp whose bounds both
+            // fail runs the float32 chain.
+            bool exact = false;
+            if (k_abs_sum != nullptr) {
+                // largest and summed 2^shift of the row
+                float smax = 0.0f, ssum = 0.0f;
+                if (row_ok) {
+                    if (qs_stride) {
+                        // the row's chunk scales, 16 bytes at a time and four loads in flight where the row allows
+                        int c = 0;
+                        float m0 = 0.0f, m1 = 0.0f, m2 = 0.0f, m3 = 0.0f, t0 = 0.0f, t1 = 0.0f, t2 = 0.0f, t3 = 0.0f;
+                        if ((reinterpret_cast<uintptr_t>(qs_row) & 15) == 0) {
+                            const float4* q4 = reinterpret_cast<const float4*>(qs_row);
+                            for (; c + 16 <= chunks; c += 16) {
+                                const float4 a = __ldg(q4 + (c >> 2)), b4 = __ldg(q4 + (c >> 2) + 1);
+                                const float4 d = __ldg(q4 + (c >> 2) + 2), e4 = __ldg(q4 + (c >> 2) + 3);
+                                m0 = fmaxf(m0, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+                                m1 = fmaxf(m1, fmaxf(fmaxf(b4.x, b4.y), fmaxf(b4.z, b4.w)));
+                                m2 = fmaxf(m2, fmaxf(fmaxf(d.x, d.y), fmaxf(d.z, d.w)));
+                                m3 = fmaxf(m3, fmaxf(fmaxf(e4.x, e4.y), fmaxf(e4.z, e4.w)));
+                                t0 += (a.x + a.y) + (a.z + a.w);
+                                t1 += (b4.x + b4.y) + (b4.z + b4.w);
+                                t2 += (d.x + d.y) + (d.z + d.w);
+                                t3 += (e4.x + e4.y) + (e4.z + e4.w);
+                            }
+                            for (; c + 4 <= chunks; c += 4) {
+                                const float4 a = __ldg(q4 + (c >> 2));
+                                m0 = fmaxf(m0, fmaxf(fmaxf(a.x, a.y), fmaxf(a.z, a.w)));
+                                t0 += (a.x + a.y) + (a.z + a.w);
+                            }
+                        }
+                        for (; c < chunks; ++c) {
+                            const float v1 = __ldg(qs_row + c);
+                            m0 = fmaxf(m0, v1);
+                            t0 += v1;
+                        }
+                        smax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+                        ssum = (t0 + t1) + (t2 + t3);
+                    } else {
+                        smax = __ldg(qs_row);
+                        ssum = smax * static_cast<float>(chunks);
+                    }
+                }
+                // of the warp's key rows: the largest sum of |k| over a row and over one 256-element chunk
+                float ktot = 0.0f, kchk = 0.0f;
+                if (lane * 4 < kCols) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int col = n0 + col0 + lane * 4 + e;
+                        if (col < R) {
+                            ktot = fmaxf(ktot, __ldg(k_abs_sum + col));
+                            kchk = fmaxf(kchk, __ldg(k_abs_sum + R + col));
+                        }
+                    }
+                }
+                // non-negative floats order like their bit patterns; an infinity anywhere fails the test
+                const float su = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(smax)));
+                const float tu = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(ssum)));
+                const float ku = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(ktot)));
+                const float cu = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(kchk)));
+                // the sums above round (relative 2^-24 per addition, at most a few hundred additions): 0.999 covers it
+                exact = fminf(su * ku, tu * cu) * q_abs_max < 16777216.0f * 0.999f;
+            }
+
             for (int c = 0; c < chunks && ok; ++c, ++cc) {
                 const int b = cc % kAccBufs;
                 const uint32_t tph = static_cast<uint32_t>(cc / kAccBufs) & 1u;
                 const float qscale = qs_stride ? __ldg(qs_row + c) : __ldg(qs_row);
+                const int qmul = exact ? __float2int_rn(qscale) : 0;
                 if (!wait_or_abort(tfull_bar(b), tph, actx, 4)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
@@ -431,12 +502,24 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                         __syncwarp();
                         if (lane == 0) mbar_arrive_cluster(leader_tempty0 + 8u * b);
                     }
+                    if (exact) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
+                        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            if (h * 32 + e < wsp)
-                                acc[c0 + h * 32 + e] = __fmaf_rn(int_to_float_exact(v[h][e]), qscale, acc[c0 + h * 32 + e]);
+                            for (int e = 0; e < 32; ++e) {
+                                if (h * 32 + e < wsp)
+                                    acc[c0 + h * 32 + e] =
+                                        __int_as_float(v[h][e] * qmul + __float_as_int(acc[c0 + h * 32 + e]));
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                if (h * 32 + e < wsp)
+                                    acc[c0 + h * 32 + e] = __fmaf_rn(int_to_float_exact(v[h][e]), qscale, acc[c0 + h * 32 + e]);
+                            }
                         }
                     }
                     if (DBG) {
@@ -455,6 +538,12 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 }
             }
             if (!ok) break;
+            if (exact) {
+                // the int32 sums (below 2^24 in magnitude) as floats: what the float32 chain would hold
+#pragma unroll
+                for (int j = 0; j < kCols; ++j) acc[j] = static_cast<float>(__float_as_int(acc[j]));
+                if (lane == 0) atomicAdd(&g_exact_int_tiles, 1ull);
+            }
 
             // ---- tile result: out = (acc * bw0[r]) * scale_inv ----
             // A lane owns a row; 32 x 32 blocks go through this warp's 4 KB of smem (16-byte chunks

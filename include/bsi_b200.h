@@ -185,6 +185,22 @@ int bsi_b200_peer_close(void* peer_ptr);
  * 64 + the missing rank (bsi_b200_device_status), so a lost rank cannot hang the GPU. */
 int bsi_b200_peer_barrier(uint32_t* const* flags, int rank, int n, int64_t timeout_ms, bsi_stream_t stream);
 
+/* Optional bounds for a key image. The chunk terms of the dot, I_c * 2^shift, are integers; while every prefix of
+ * their sum stays below 2^24 in magnitude no float32 addition of the reference's chain rounds, and accumulating the
+ * terms as int32 gives the same bits with a third of the epilogue's arithmetic. A prefix is bounded by
+ * query_abs_max x (largest 2^shift of the query row) x (sum of |k| over key row r) and by query_abs_max x (sum of the
+ * row's 2^shift) x (largest sum of |k| over one 256-element chunk of key row r). With key_abs_sum (device, float32
+ * [2, R]: the R row sums, then the R chunk maxima) registered for k8, the tensor-core dots that are handed this k8
+ * with this R test the bounds per tile and take the integer route where one holds (the float32 chain elsewhere;
+ * results identical either way).
+ * query_abs_max: largest magnitude of a query integer (64 for 7-bit fixed queries, 128 when unknown). Registering
+ * again replaces the entry; unregister before the arrays are freed. BSI_B200_EXACT_INT=0 switches the route off. */
+int bsi_b200_register_key_bounds(const int8_t* k8, const float* key_abs_sum, int64_t R, int query_abs_max);
+int bsi_b200_unregister_key_bounds(const int8_t* k8);
+/* Test hook: number of (warp, tile) pairs of the paired tensor-core kernel that took the integer route since the
+ * last call on this device; synchronises and clears the counter. */
+int bsi_b200_debug_exact_int_tiles(unsigned long long* count_out);
+
 /* Linear whose finished output is re-quantised for the next linear inside the epilogue, so that the
  * layer-type [Q, R] matrix is never written: y = activation(cast(out) + cast(bias)) in layer_dtype
  * (BSI_DTYPE_F16 / BF16) is what bsi_b200_linear_i8_act would store; here every 256-column chunk of y

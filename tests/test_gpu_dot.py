@@ -270,3 +270,88 @@ def test_linear_requant_reports_values_it_cannot_express():
     assert bsi_ops.device_status() == 48
     assert bsi_ops.device_status() == 0          # reading clears it
     assert not out_q8.any()
+
+
+def _key_bounds(k8):
+    """[2, R] float32: sum of |k| over each key row, then the largest such sum over one 256-element chunk."""
+    per_chunk = k8.to(torch.int32).abs().view(k8.shape[0], -1, 256).sum(2)
+    return torch.stack([per_chunk.sum(1), per_chunk.amax(1)]).to(torch.float32).contiguous()
+
+
+@pytest.mark.parametrize("engine", [3256, 3224, 3128, 3064])
+def test_exact_integer_route_gives_the_float_chain_bits(engine):
+    """With the row sums of |k| registered for a key image, tiles whose prefix sums provably stay below 2^24
+    accumulate in int32; tiles that fail the bound keep the float32 chain. Same bits either way, and the same as
+    without the registration and as the checker."""
+    L = capi.lib()
+    Q, R, D = 600, 1100, 1024
+    g = torch.Generator().manual_seed(engine)
+    q = torch.randn(Q, D, generator=g)
+    q[256:512] *= 3.0e4                      # tile rows 256..511: chunk shifts around 15, the bound fails
+    q[5, 300] = 900.0                        # a lone outlier in a tile that passes
+    k = torch.randn(R, D, generator=g) * 0.02
+    k[700] = 0.0                             # an all-zero key row
+    qa, kb, _ = _prepare(q, k)
+    want, _ = _oracle(q, k)
+    capi.exact_int_tiles()
+    plain = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), engine)
+    assert capi.exact_int_tiles() == 0
+    abs_sum = _key_bounds(kb["q8"])
+    capi.check(L.bsi_b200_register_key_bounds(capi.ptr(kb["q8"]), capi.ptr(abs_sum), R, 64))
+    try:
+        got = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), engine)
+        n_int = capi.exact_int_tiles()
+        bn = engine - 3000
+        tiles_n = -(-R // bn)
+        # 8 epilogue warps per tile pair... every (warp, tile) with rows outside 256..511 passes, the others fail
+        assert 0 < n_int < 3 * tiles_n * 16
+        # the debug dump of the per-chunk integers is unaffected
+        got_dbg, iacc = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), engine, want_iacc=True)
+        assert torch.equal(got_dbg, got)
+        capi.exact_int_tiles()
+    finally:
+        capi.check(L.bsi_b200_unregister_key_bounds(capi.ptr(kb["q8"])))
+    _assert_bits(plain, want)
+    _assert_bits(got, want)
+    H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), engine)
+    assert capi.exact_int_tiles() == 0       # unregistered again
+    assert capi.device_status() == 0
+
+
+def test_exact_integer_route_row_scale_and_16bit_outputs():
+    """The same route under a single scale per query row and in the layer epilogues (cast + bias, re-quantisation)."""
+    import ctypes as C
+    L = capi.lib()
+    Q, R, D = 512, 768, 512
+    q, k = _inputs.c1(Q=Q, R=R, D=D, seed=5)
+    qa, kb, _ = _prepare(q, k, chunk_mode=False)
+    want, _ = _oracle(q, k, chunk_mode=False)
+    abs_sum = _key_bounds(kb["q8"])
+    plain = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), 3256)
+    qc, _, _ = _prepare(q, k)
+    chunks = D // 256
+    bias = torch.linspace(-1, 1, R, device=DEV)
+
+    def linear(code_dtype):
+        y = torch.empty(Q, R, dtype=code_dtype, device=DEV)
+        code = capi.DTYPE_F16 if code_dtype == torch.float16 else capi.DTYPE_BF16
+        capi.check(L.bsi_b200_linear_i8_act(capi.ptr(qc["q8"]), qc["q8"].shape[1], capi.ptr(qc["scales"]), chunks,
+                                            capi.ptr(kb["q8"]), kb["q8"].shape[1], capi.ptr(kb["scales"]), capi.ptr(bias),
+                                            Q, R, chunks, C.c_float(float(o.scale_inv(2))), capi.ptr(y), R, code, 1,
+                                            capi.stream_ptr()))
+        return y
+
+    y_plain = [linear(torch.float16), linear(torch.bfloat16)]
+    capi.exact_int_tiles()
+    capi.check(L.bsi_b200_register_key_bounds(capi.ptr(kb["q8"]), capi.ptr(abs_sum), R, 64))
+    try:
+        got = H.dot_i8(qa["q8"], qa["scales"], kb["q8"], kb["scales"], o.scale_inv(2), 3256)
+        assert capi.exact_int_tiles() > 0
+        y_int = [linear(torch.float16), linear(torch.bfloat16)]
+        assert capi.exact_int_tiles() > 0
+    finally:
+        capi.check(L.bsi_b200_unregister_key_bounds(capi.ptr(kb["q8"])))
+    _assert_bits(plain, want)
+    _assert_bits(got, want)
+    for a, b in zip(y_plain, y_int):
+        assert torch.equal(a, b)
