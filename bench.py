@@ -642,10 +642,12 @@ def main():
         sets.append(dict(a8=qt["q8"].clone(), qs=qt["scales"].clone(), k8=kt["q8"].clone(),
                          bw0=kt["scales"].clone(), out=torch.empty(Q, R, dtype=torch.float32, device=dev)))
     # every operand set stands for a key set of its own: give each the bounds its builder would have registered
-    register_bounds(L, capi, sets, kt, R)
+    register_bounds(L, capi, sets, kt, R, qt)
     engine = {"tcgen05": capi.ENGINE_TCGEN05, "simt": capi.ENGINE_SIMT}.get(args.engine)
     if engine is None and args.engine.startswith("tcgen05:"):
-        engine = 1000 + int(args.engine.split(":")[1])
+        engine = 1000 + int(args.engine.split(":")[1])      # single-CTA tiles of that width
+    if engine is None and args.engine.startswith("pair:"):
+        engine = 3000 + int(args.engine.split(":")[1])      # paired-CTA tiles of that width
     scale_inv = C.c_float(float(1.0 / 10.0 ** 4))
     if args.engine == "bmma":      # b1 mma.sync engine: reads the slice words, not the int8 image
         for s_ in sets:
@@ -884,20 +886,25 @@ def main():
         dist.destroy_process_group()
 
 
-def register_bounds(L, capi, sets, key_tensors, R):
-    """The bench times the C entry point on copies of one packed key set; build_bsi_keys_cuda registers the row sums
-    of |k| for the image it owns (they let a dot accumulate in integers where that is provably exact), so the
-    copies get the same registration -- what a user's key sets have."""
+def register_bounds(L, capi, sets, key_tensors, R, query_tensors=None):
+    """The bench times the C entry point on copies of one packed key set and one packed query batch. The bsi_ops
+    entry points register, for the images they own, the sums that let a dot accumulate in integers where that is
+    provably exact (row sums of the keys at build time, chunk sums of squares of the queries around each dot), so
+    the copies get the same registration -- what a user's capsules have."""
     if "abs_sum" not in key_tensors:
         return
     for s in sets:
         capi.check(L.bsi_b200_register_key_bounds(capi.ptr(s["k8"]), capi.ptr(key_tensors["abs_sum"]), R, 64),
                    "bsi_b200_register_key_bounds")
+        if query_tensors is not None and "sq_norms" in query_tensors:
+            capi.check(L.bsi_b200_register_query_bounds(capi.ptr(s["a8"]), capi.ptr(query_tensors["sq_norms"]),
+                                                        query_tensors["sq_norms"].shape[1]), "bsi_b200_register_query_bounds")
 
 
 def unregister_bounds(L, capi, sets):
     for s in sets:
         L.bsi_b200_unregister_key_bounds(capi.ptr(s["k8"]))
+        L.bsi_b200_unregister_query_bounds(capi.ptr(s["a8"]))
 
 
 def time_fc2(dev, ops, L, capi):
@@ -919,7 +926,7 @@ def time_fc2(dev, ops, L, capi):
     sets = [dict(a8=qt["q8"].clone(), qs=qt["scales"].clone(), k8=kt["q8"].clone(), bw0=kt["scales"].clone(),
                  out=torch.empty(Q, R, dtype=torch.float32, device=dev)) for _ in range(nsets)]
     scale_inv = C.c_float(float(1.0 / 10.0 ** 4))
-    register_bounds(L, capi, sets, kt, R)
+    register_bounds(L, capi, sets, kt, R, qt)
 
     def step(i):
         s = sets[i % nsets]

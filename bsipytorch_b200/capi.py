@@ -28,6 +28,9 @@ SIGNATURES = {
     "bsi_b200_quantize_pack_clip": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _i64, _vp]),
     "bsi_b200_decimal_absmax": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _vp, _vp, _vp]),
     "bsi_b200_pack_plain": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _vp, _vp, _vp, _i64, _vp]),
+    "bsi_b200_quantize_pack_norms": (_i32, [_vp, _i32, _i64, _i64, _i64, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _i64, _vp, _vp]),
+    "bsi_b200_register_query_bounds": (_i32, [_vp, _vp, _i64]),
+    "bsi_b200_unregister_query_bounds": (_i32, [_vp]),
     "bsi_b200_register_key_bounds": (_i32, [_vp, _vp, _i64, _i32]),
     "bsi_b200_unregister_key_bounds": (_i32, [_vp]),
     "bsi_b200_debug_exact_int_tiles": (_i32, [_vp]),

@@ -112,6 +112,7 @@ struct PackedBatch {
     at::Tensor slice_weights;  // [rows, S] float32
     at::Tensor scales;         // [rows, chunks] (chunk mode) or [rows] (row mode) float32: 2^shift
     at::Tensor q8;             // [rows, ld8] int8
+    at::Tensor sq_norms;       // [rows, chunks] float32 (chunk mode): (2^shift)^2 * sum of squares of the chunk's integers
     bool chunk_mode = false;
     bool variable = false;     // variable-slice mode: no shift, q8 holds the integers (their low digit when q8_hi is set)
     at::Tensor q8_hi;          // [rows, ld8] int8: v = 128 * q8_hi + q8 (only when some |v| > 127)
@@ -129,8 +130,8 @@ struct PrebuiltBSIKeysCUDA {
     PackedBatch b;
     int64_t num_keys = 0;
     float threshold = 0.2f;
-    at::Tensor abs_sum;      // [2, num_keys] float32: sum of |k| over each row of the int8 image, then the largest
-                             // such sum over one 256-element chunk of the row (integers below 2^24: exact)
+    at::Tensor abs_sum;      // [3, num_keys] float32: sum of |k| over each row of the int8 image, the largest such sum
+                             // over one 256-element chunk of the row, the row's sum of k^2
     ~PrebuiltBSIKeysCUDA() {
         if (abs_sum.defined() && b.q8.defined()) bsi_b200_unregister_key_bounds(b.q8.data_ptr<int8_t>());
     }
@@ -138,8 +139,10 @@ struct PrebuiltBSIKeysCUDA {
     void compute_bounds() {
         if (!b.q8.defined() || b.q8.numel() == 0 || b.variable) return;
         c10::cuda::CUDAGuard guard(b.q8.device());
-        at::Tensor per_chunk = b.q8.to(at::kInt).abs_().view({b.q8.size(0), -1, 256}).sum(2);   // [R, chunks]
-        abs_sum = at::stack({per_chunk.sum(1), per_chunk.amax(1)}, 0).to(at::kFloat).contiguous();
+        at::Tensor k32 = b.q8.to(at::kInt);
+        at::Tensor squares = (k32 * k32).sum(1);                                             // at most 2^24 for 16384 x 32^2
+        at::Tensor per_chunk = k32.abs_().view({b.q8.size(0), -1, 256}).sum(2);              // [R, chunks]
+        abs_sum = at::stack({per_chunk.sum(1), per_chunk.amax(1), squares}, 0).to(at::kFloat).contiguous();
     }
     // Called before every dot on these keys: the bound depends on the width of the queries of that dot.
     void register_bounds(int query_bits) const {
@@ -147,6 +150,23 @@ struct PrebuiltBSIKeysCUDA {
         const int qmax = (query_bits >= 2 && query_bits <= 8) ? (1 << (query_bits - 1)) : 128;
         bsi_b200_register_key_bounds(b.q8.data_ptr<int8_t>(), abs_sum.data_ptr<float>(), num_keys, qmax);
     }
+};
+
+// Registers a query batch's chunk sums of squares for the duration of one dot call (the Cauchy-Schwarz side of the
+// exact-integer route); the kernel gets the pointers at launch, so the entry can go when the call returns.
+struct ScopedQueryBounds {
+    const int8_t* a8 = nullptr;
+    explicit ScopedQueryBounds(const PackedBatch& qb) {
+        if (qb.sq_norms.defined() && qb.chunk_mode && qb.q8.defined() && qb.q8.numel() > 0) {
+            a8 = qb.q8.data_ptr<int8_t>();
+            bsi_b200_register_query_bounds(a8, qb.sq_norms.data_ptr<float>(), qb.sq_norms.size(1));
+        }
+    }
+    ~ScopedQueryBounds() {
+        if (a8 != nullptr) bsi_b200_unregister_query_bounds(a8);
+    }
+    ScopedQueryBounds(const ScopedQueryBounds&) = delete;
+    ScopedQueryBounds& operator=(const ScopedQueryBounds&) = delete;
 };
 
 struct PrebuiltBSIQueryBatchCUDA {
@@ -211,6 +231,7 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
     if (chunk_mode) b.scales = at::ones({b.rows, std::max<int64_t>(b.chunks, 0)}, opt(at::kFloat));
     else b.scales = at::ones({b.rows}, opt(at::kFloat));
     b.q8 = at::empty({b.rows, ld8}, opt(at::kChar));
+    if (chunk_mode && b.rows > 0 && b.d > 0) b.sq_norms = at::empty({b.rows, b.chunks}, opt(at::kFloat));
     if (b.rows == 0 || b.d == 0) {
         b.q8.zero_();
         if (lean) b.words = at::zeros({b.rows, bits, b.W}, opt(at::kLong));
@@ -225,12 +246,13 @@ PackedBatch pack(const at::Tensor& input, int decimal_places, int bits, bool chu
         cudaEventCreate(&e1);
         cudaEventRecord(e0, stream.stream());
     }
-    check_status(bsi_b200_quantize_pack_clip(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, bits,
-                                             chunk_mode ? 1 : 0, clip_k,
-                                             lean ? nullptr : reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
-                                             b.scales.data_ptr<float>(), nullptr, b.q8.data_ptr<int8_t>(), ld8,
-                                             current_stream()),
-                 "bsi_b200_quantize_pack_clip");
+    check_status(bsi_b200_quantize_pack_norms(x.data_ptr(), dtype_code(x), b.rows, b.d, b.d, decimal_places, bits,
+                                              chunk_mode ? 1 : 0, clip_k,
+                                              lean ? nullptr : reinterpret_cast<uint64_t*>(b.words.data_ptr<int64_t>()),
+                                              b.scales.data_ptr<float>(), nullptr, b.q8.data_ptr<int8_t>(), ld8,
+                                              b.sq_norms.defined() ? b.sq_norms.data_ptr<float>() : nullptr,
+                                              current_stream()),
+                 "bsi_b200_quantize_pack_norms");
     if (profile) {
         cudaEventRecord(e1, stream.stream());
         cudaEventSynchronize(e1);
@@ -521,6 +543,7 @@ py::tuple run_dot(const PackedBatch& qb, const PrebuiltBSIKeysCUDA& keys, bool w
     const int engine = engine_from_env();
     const int64_t qs_stride = qb.chunk_mode ? qb.chunks : 0;
     keys.register_bounds(qb.variable ? 8 : qb.S);
+    ScopedQueryBounds query_bounds(qb);
     if (qb.variable || keys.b.variable) {
         TORCH_CHECK(engine != BSI_ENGINE_BMMA, "the b1 mma.sync engine reads fixed-bit slices; variable-slice operands use the int8 engines");
         TORCH_CHECK(!want_iacc, "the per-chunk accumulator dump is defined for the fixed-bit mode");
@@ -616,6 +639,15 @@ PackedBatch batch_from_list(const py::list& caps) {
     b.slice_weights = at::stack(weights).contiguous();
     b.scales = at::stack(scales).contiguous();
     b.q8 = at::stack(q8).contiguous();
+    {
+        bool all = true;
+        for (int64_t i = 0; i < Q; ++i) all = all && rows[i]->parent->sq_norms.defined();
+        if (all && Q > 0) {
+            std::vector<at::Tensor> n2;
+            for (int64_t i = 0; i < Q; ++i) n2.push_back(rows[i]->parent->sq_norms[rows[i]->row]);
+            b.sq_norms = at::stack(n2).contiguous();
+        }
+    }
     return b;
 }
 
@@ -705,6 +737,7 @@ at::Tensor bsi_linear_forward(torch::Tensor x2d, py::capsule keyset_cuda_cap, c1
     const int code = yt == at::kHalf ? BSI_DTYPE_F16 : (yt == at::kBFloat16 ? BSI_DTYPE_BF16 : BSI_DTYPE_F32);
     if (fused) {
         keys->register_bounds(qb.S);
+        ScopedQueryBounds query_bounds(qb);
         check_status(bsi_b200_linear_i8(qb.q8.data_ptr<int8_t>(), qb.q8.size(1), qb.scales.data_ptr<float>(),
                                         qb.chunk_mode ? qb.chunks : 0, keys->b.q8.data_ptr<int8_t>(),
                                         keys->b.q8.size(1), keys->b.scales.data_ptr<float>(), bptr, Q, R, qb.chunks,
@@ -972,6 +1005,7 @@ py::dict debug_batch(const PackedBatch& b) {
     d["slice_weights"] = b.slice_weights;
     d["scales"] = b.scales;
     d["q8"] = b.q8;
+    if (b.sq_norms.defined()) d["sq_norms"] = b.sq_norms;
     d["chunk_mode"] = b.chunk_mode;
     d["S"] = b.S;
     d["W"] = b.W;

@@ -31,7 +31,16 @@ bool pdl_enabled() {
 namespace {
 std::mutex g_bounds_mu;
 std::unordered_map<const void*, KeyBounds> g_bounds;
+std::unordered_map<const void*, QueryBounds> g_query_bounds;
 }  // namespace
+
+bool lookup_query_bounds(const void* a8, QueryBounds* out) {
+    std::lock_guard<std::mutex> lock(g_bounds_mu);
+    auto it = g_query_bounds.find(a8);
+    if (it == g_query_bounds.end()) return false;
+    *out = it->second;
+    return true;
+}
 
 bool lookup_key_bounds(const void* k8, KeyBounds* out) {
     const char* e = getenv("BSI_B200_EXACT_INT");      // 0 switches the integer accumulation off (A/B comparisons)
@@ -113,5 +122,23 @@ extern "C" int bsi_b200_unregister_key_bounds(const int8_t* k8) {
     using namespace bsi;
     std::lock_guard<std::mutex> lock(g_bounds_mu);
     g_bounds.erase(k8);
+    return BSI_OK;
+}
+
+extern "C" int bsi_b200_register_query_bounds(const int8_t* a8, const float* sq_norms, int64_t stride) {
+    using namespace bsi;
+    if (a8 == nullptr || sq_norms == nullptr || stride <= 0) {
+        set_error("register_query_bounds: bad argument");
+        return BSI_ERR_INVALID;
+    }
+    std::lock_guard<std::mutex> lock(g_bounds_mu);
+    g_query_bounds[a8] = QueryBounds{sq_norms, stride};
+    return BSI_OK;
+}
+
+extern "C" int bsi_b200_unregister_query_bounds(const int8_t* a8) {
+    using namespace bsi;
+    std::lock_guard<std::mutex> lock(g_bounds_mu);
+    g_query_bounds.erase(a8);
     return BSI_OK;
 }

@@ -64,11 +64,16 @@ struct RequantDst {
 // Bounds registered for a key image (bsi_b200_register_key_bounds): with them a dot can tell, per tile, that every
 // prefix of a chunk sum stays below 2^24 in magnitude, where integer accumulation gives the float32 chain's bits.
 struct KeyBounds {
-    const float* abs_sum;    // [rows] device: sum of |k| over each key row
+    const float* abs_sum;    // [3, rows] device: sum of |k| per key row, largest sum over one chunk, sum of k^2
     int64_t rows;
     float query_abs_max;     // largest magnitude of a query integer in dots against these keys
 };
 bool lookup_key_bounds(const void* k8, KeyBounds* out);   // false: none registered (or BSI_B200_EXACT_INT=0)
+struct QueryBounds {
+    const float* sq_norms;   // per (row, chunk): (2^shift)^2 * sum of squares of the chunk's integers
+    int64_t stride;          // floats per row
+};
+bool lookup_query_bounds(const void* a8, QueryBounds* out);
 
 // True unless BSI_B200_PDL=0: the dot kernels are launched with programmatic stream serialisation (their set-up
 // may overlap the tail of a dot kernel right before them on the stream).

@@ -447,7 +447,8 @@ template <int BN, bool DBG, typename OutT, bool REQ = false>
 int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
                 const float* qs, int64_t qs_stride, const float* bw0, const float* bias, int Q, int R, int chunks,
                 float scale_inv, void* out, int64_t ldo, int32_t* dbg, const ScatterDst& scatter,
-                const RequantDst& requant, const float* k_abs_sum, float q_abs_max, cudaStream_t stream) {
+                const RequantDst& requant, const float* k_abs_sum, float q_abs_max, const float* q_sq, int64_t q_sq_stride,
+                cudaStream_t stream) {
     using C = pair::Cfg<BN>;
     static int max_clusters[64] = {0};   // per instantiation
     int dev = 0;
@@ -483,7 +484,7 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, int vector_store,
     cfg.gridDim = dim3(2 * pairs, 1, 1);
     BSI_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::dot_i8_tcgen05_pair_kernel<BN, DBG, OutT, REQ>, ma, mb, vector_store, qs,
                                     qs_stride, bw0, bias, Q, R, chunks, tiles_m, tiles_total, scale_inv, out, ldo, dbg, scatter, requant,
-                                    k_abs_sum, q_abs_max));
+                                    k_abs_sum, q_abs_max, q_sq, q_sq_stride));
     return check_launch("dot_i8 tcgen05 pair launch");
 }
 
@@ -576,13 +577,20 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     KeyBounds kb = {};
     const float* kabs = nullptr;
     float qabs = 0.0f;
+    const float* qsq = nullptr;
+    int64_t qsq_stride = 0;
     if (lookup_key_bounds(k8, &kb) && kb.rows == R) {
         kabs = kb.abs_sum;
         qabs = kb.query_abs_max;
+        QueryBounds qb = {};
+        if (qs_stride != 0 && lookup_query_bounds(a8, &qb) && qb.stride >= chunks) {
+            qsq = qb.sq_norms;
+            qsq_stride = qb.stride;
+        }
     }
 #define BSI_PAIR_T(BN_, DBG_, T_)                                                                              \
     launch_pair<BN_, DBG_, T_>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv, out, ldo,  \
-                               dbg_iacc, scatter, requant, kabs, qabs, stream)
+                               dbg_iacc, scatter, requant, kabs, qabs, qsq, qsq_stride, stream)
 #define BSI_PAIR(BN_)                                                                   \
     (y_dtype == BSI_DTYPE_F16    ? BSI_PAIR_T(BN_, false, __half)                       \
      : y_dtype == BSI_DTYPE_BF16 ? BSI_PAIR_T(BN_, false, __nv_bfloat16)                \
@@ -591,9 +599,10 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     if (requant.n > 0) {
         if (y_dtype == BSI_DTYPE_F16)
             return launch_pair<256, false, __half, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv,
-                                                         out, ldo, nullptr, scatter, requant, kabs, qabs, stream);
+                                                         out, ldo, nullptr, scatter, requant, kabs, qabs, qsq, qsq_stride, stream);
         return launch_pair<256, false, __nv_bfloat16, true>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c,
-                                                            scale_inv, out, ldo, nullptr, scatter, requant, kabs, qabs, stream);
+                                                            scale_inv, out, ldo, nullptr, scatter, requant, kabs, qabs, qsq,
+                                                            qsq_stride, stream);
     }
 #define BSI_PAIR_F32(BN_) (dbg_iacc ? BSI_PAIR_T(BN_, true, float) : BSI_PAIR_T(BN_, false, float))
     switch (bn) {

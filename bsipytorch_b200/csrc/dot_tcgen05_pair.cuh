@@ -210,7 +210,8 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
     const float* __restrict__ qs, int64_t qs_stride, const float* __restrict__ bw0,
     const float* __restrict__ bias, int Q, int R, int chunks, int tiles_m, int tiles_total, float scale_inv,
     void* __restrict__ out, int64_t ldo, int32_t* __restrict__ dbg_iacc, const ScatterDst scatter,
-    const RequantDst requant, const float* __restrict__ k_abs_sum, float q_abs_max) {
+    const RequantDst requant, const float* __restrict__ k_abs_sum, float q_abs_max,
+    const float* __restrict__ q_sq, int64_t q_sq_stride) {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     constexpr int kCols = BN / 2;              // accumulator columns per epilogue warp: a multiple of 16
@@ -408,9 +409,10 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
             // acc += I_c << shift in int32 gives the same bits. With A the largest query magnitude, a prefix is at
             // most A x (largest 2^shift of the row) x (sum of |k| over the key row), and also at most
             // A x (sum of the row's 2^shift) x (largest sum of |k| over one chunk of the key row); the key sums come
-            // from the caller (k_abs_sum: R row sums, then R chunk maxima; null: not available). The test is made
-            // for the warp's 32 rows x kCols columns at once, so the branch is uniform; a warp whose bounds both
-            // fail runs the float32 chain.
+            // from the caller (k_abs_sum: R row sums, then R chunk maxima, then R sums of squares; null: not
+            // available). Where both fail and the query image carries its chunk sums of squares (q_sq), the
+            // Cauchy-Schwarz product of the two rows' L2 norms is tried. The test is made for the warp's 32 rows x
+            // kCols columns at once, so the branch is uniform; a warp whose bounds all fail runs the float32 chain.
             bool exact = false;
             if (k_abs_sum != nullptr) {
                 // largest and summed 2^shift of the row
@@ -471,6 +473,32 @@ __global__ void __launch_bounds__(kThreads, 1) dot_i8_tcgen05_pair_kernel(
                 const float cu = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(kchk)));
                 // the sums above round (relative 2^-24 per addition, at most a few hundred additions): 0.999 covers it
                 exact = fminf(su * ku, tu * cu) * q_abs_max < 16777216.0f * 0.999f;
+                if (!exact && q_sq != nullptr) {
+                    // Cauchy-Schwarz: |prefix|^2 <= (sum of squares of the de-shifted query row) x (sum of k^2)
+                    float u2 = 0.0f;
+                    if (row_ok) {
+                        const float* nrow = q_sq + static_cast<int64_t>(row) * q_sq_stride;
+                        float a0 = 0.0f, a1 = 0.0f;
+                        int c = 0;
+                        for (; c + 2 <= chunks; c += 2) {
+                            a0 += __ldg(nrow + c);
+                            a1 += __ldg(nrow + c + 1);
+                        }
+                        if (c < chunks) a0 += __ldg(nrow + c);
+                        u2 = a0 + a1;
+                    }
+                    float k2 = 0.0f;
+                    if (lane * 4 < kCols) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int col = n0 + col0 + lane * 4 + e;
+                            if (col < R) k2 = fmaxf(k2, __ldg(k_abs_sum + 2 * static_cast<int64_t>(R) + col));
+                        }
+                    }
+                    const float u2w = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(u2)));
+                    const float k2w = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(k2)));
+                    exact = u2w * k2w < 281474976710656.0f * 0.999f;      // 2^48
+                }
             }
 
             for (int c = 0; c < chunks && ok; ++c, ++cc) {

@@ -226,7 +226,10 @@ __device__ __forceinline__ void generic_unit(const T* __restrict__ x, int64_t un
                                              double dec_scale, uint32_t dec_mult, int bits, int64_t chunks, int64_t W,
                                              u64* __restrict__ words, float* __restrict__ scales,
                                              int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8,
-                                             bool vec, int lane, float clip_k = 0.0f) {
+                                             bool vec, int lane, float clip_k = 0.0f,
+                                             float* __restrict__ sq_norms = nullptr) {
+    // no sum of squares from this path: infinity makes a dot's exactness test that reads it fail safely
+    if (sq_norms != nullptr && lane == 0) sq_norms[unit] = __int_as_float(0x7f800000);
     const int64_t row = unit / chunks;
     const int64_t chunk = unit - row * chunks;
     float f[8];
@@ -262,13 +265,14 @@ template <typename T>
 __global__ void __launch_bounds__(256) quantize_pack_chunk_generic_kernel(
     const T* __restrict__ x, int64_t rows, int64_t D, int64_t ldx, double dec_scale, uint32_t dec_mult, int bits,
     int64_t chunks, int64_t W, u64* __restrict__ words, float* __restrict__ scales,
-    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok, float clip_k) {
+    int32_t* __restrict__ shifts, int8_t* __restrict__ q8, int64_t ld8, int vec_ok, float clip_k,
+    float* __restrict__ sq_norms) {
     const int lane = threadIdx.x & 31;
     const int64_t total = rows * chunks;
     for (int64_t unit = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); unit < total;
          unit += static_cast<int64_t>(gridDim.x) * 8)
         generic_unit<T>(x, unit, D, ldx, dec_scale, dec_mult, bits, chunks, W, words, scales, shifts, q8, ld8,
-                        vec_ok != 0, lane, clip_k);
+                        vec_ok != 0, lane, clip_k, sq_norms);
 }
 
 // Fast path of one chunk: true when the chunk was quantised and stored, false when it needs the generic
@@ -317,10 +321,19 @@ template <typename T, bool kWords, bool kQ8>
 __device__ __forceinline__ bool fast_chunk(const float (&f)[8], uint32_t unit, uint32_t q8_off, uint32_t word_off,
                                            bool word_ok, int lane, uint32_t dec_mult, int bits, uint32_t slice_bytes,
                                            u64* __restrict__ words, float* __restrict__ scales,
-                                           int32_t* __restrict__ shifts, int8_t* __restrict__ q8) {
+                                           int32_t* __restrict__ shifts, int8_t* __restrict__ q8,
+                                           float* __restrict__ sq_norms) {
     int shift;
     u64 packed;
     if (!fast_quantise<T>(f, dec_mult, bits, shift, packed)) return false;
+    if (sq_norms != nullptr) {
+        // sum of squares of the chunk's de-shifted integers, (2^shift)^2 * sum a^2: an exact float (the integer
+        // sum is at most 256 * 128^2 = 2^22), which a dot's exactness test turns into a Cauchy-Schwarz bound
+        int n2 = __dp4a(static_cast<int>(static_cast<uint32_t>(packed)), static_cast<int>(static_cast<uint32_t>(packed)), 0);
+        n2 = __dp4a(static_cast<int>(static_cast<uint32_t>(packed >> 32)), static_cast<int>(static_cast<uint32_t>(packed >> 32)), n2);
+        n2 = __reduce_add_sync(0xffffffffu, n2);
+        if (lane == 0) sq_norms[unit] = static_cast<float>(n2) * __uint_as_float(static_cast<uint32_t>(127 + 2 * shift) << 23);
+    }
     if (lane == 0) {
         scales[unit] = __uint_as_float(static_cast<uint32_t>(127 + shift) << 23);   // 2^shift
         if (shifts != nullptr) shifts[unit] = shift;
@@ -401,7 +414,7 @@ template <typename T, bool kDense, bool kWords, bool kQ8>
 __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_chunk_fast_kernel(
     const T* __restrict__ x, FastGeom g, double dec_scale, uint32_t dec_mult, int bits,
     u64* __restrict__ words, float* __restrict__ scales, int32_t* __restrict__ shifts, int8_t* __restrict__ q8,
-    int vec_ok) {
+    int vec_ok, float* __restrict__ sq_norms) {
     __shared__ uint32_t slow_queue[8][kSlowQueue];
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -439,7 +452,7 @@ __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_chunk_
         const uint32_t word_off = kWords ? p.row * g.row_bytes + p.chunk * 32u + lane_word : 0u;
         const bool word_ok = kDense || p.chunk * 4u + (lane >> 3) < g.W;
         if (!fast_chunk<T, kWords, kQ8>(f, p.unit, q8_off, word_off, word_ok, lane, dec_mult, bits, g.slice_bytes,
-                                        words, scales, shifts, q8)) {
+                                        words, scales, shifts, q8, sq_norms)) {
             if (nslow < kSlowQueue && lane == 0) slow_queue[warp][nslow] = p.unit;
             ++nslow;
         }
@@ -471,11 +484,11 @@ __global__ void __launch_bounds__(256, BSI_PACK_MIN_BLOCKS) quantize_pack_chunk_
     if (nslow <= kSlowQueue) {
         for (int i = 0; i < nslow; ++i)
             generic_unit<T>(x, slow_queue[warp][i], g.D, g.ldx, dec_scale, dec_mult, bits, g.chunks, g.W, words, scales,
-                            shifts, q8, ld8, vec, lane);
+                            shifts, q8, ld8, vec, lane, 0.0f, sq_norms);
     } else {
         for (uint32_t unit = first; unit < g.total; unit += stride)
             generic_unit<T>(x, unit, g.D, g.ldx, dec_scale, dec_mult, bits, g.chunks, g.W, words, scales, shifts, q8,
-                            ld8, vec, lane);
+                            ld8, vec, lane, 0.0f, sq_norms);
     }
 }
 
@@ -933,6 +946,7 @@ struct ChunkArgs {
     int vec_ok;
     cudaStream_t stream;
     float clip_k;
+    float* sq_norms;
 };
 
 template <typename T, bool kDense, bool kWords, bool kQ8>
@@ -951,7 +965,7 @@ int launch_chunk_fast(const T* x, const ChunkArgs& a) {
     g.row_bytes = static_cast<uint32_t>(a.bits * a.W * 8);
     g.slice_bytes = static_cast<uint32_t>(a.W * 8);
     quantize_pack_chunk_fast_kernel<T, kDense, kWords, kQ8><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
-        x, g, a.dec_scale, a.dec_mult, a.bits, a.words, a.scales, a.shifts, a.q8, a.vec_ok);
+        x, g, a.dec_scale, a.dec_mult, a.bits, a.words, a.scales, a.shifts, a.q8, a.vec_ok, a.sq_norms);
     return BSI_OK;
 }
 
@@ -971,7 +985,7 @@ int launch_chunk(const T* x, const ChunkArgs& a) {
         blocks = blocks < cap ? blocks : cap;
         quantize_pack_chunk_generic_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, a.stream>>>(
             x, a.rows, a.D, a.ldx, a.dec_scale, a.dec_mult, a.bits, a.chunks, a.W, a.words, a.scales, a.shifts, a.q8,
-            a.ld8, a.vec_ok, a.clip_k);
+            a.ld8, a.vec_ok, a.clip_k, a.sq_norms);
         return BSI_OK;
     }
     const bool dense = a.vec_ok && a.ldx == a.D && (a.D & 255) == 0 && (a.q8 == nullptr || a.ld8 == a.D);
@@ -1000,7 +1014,17 @@ extern "C" int bsi_b200_quantize_pack_clip(const void* x, int dtype, int64_t row
                                            int decimal_places, int bits, int chunk_mode, float clip_k,
                                            uint64_t* words, float* scales, int32_t* shifts,
                                            int8_t* q8, int64_t ld8, bsi_stream_t stream_) {
+    return bsi_b200_quantize_pack_norms(x, dtype, rows, D, ldx, decimal_places, bits, chunk_mode, clip_k, words, scales,
+                                        shifts, q8, ld8, nullptr, stream_);
+}
+
+extern "C" int bsi_b200_quantize_pack_norms(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                                            int decimal_places, int bits, int chunk_mode, float clip_k,
+                                            uint64_t* words, float* scales, int32_t* shifts,
+                                            int8_t* q8, int64_t ld8, float* sq_norms, bsi_stream_t stream_) {
     using namespace bsi;
+    if (sq_norms != nullptr && !chunk_mode)
+        return fail(BSI_ERR_UNSUPPORTED, "quantize_pack: sums of squares are per (row, chunk): chunk mode only");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if (rows < 0 || D < 0 || ldx < D) return fail(BSI_ERR_INVALID, "quantize_pack: bad rows/D/ldx");
     if (bits < 2 || bits > 8) return fail(BSI_ERR_UNSUPPORTED, "quantize_pack: bits must be in [2, 8]");
@@ -1026,7 +1050,8 @@ extern "C" int bsi_b200_quantize_pack_clip(const void* x, int dtype, int64_t row
     u64* w = reinterpret_cast<u64*>(words);
 
     if (chunk_mode) {
-        ChunkArgs a{rows, D, ldx, ld8, chunks, W, dec_scale, dec_mult, bits, w, scales, shifts, q8, vec_ok, stream, clip_k};
+        ChunkArgs a{rows, D, ldx, ld8, chunks, W, dec_scale, dec_mult, bits, w, scales, shifts, q8, vec_ok, stream, clip_k,
+                    sq_norms};
         int rc;
         if (dtype == BSI_DTYPE_F32) rc = launch_chunk<float>(static_cast<const float*>(x), a);
         else if (dtype == BSI_DTYPE_F16) rc = launch_chunk<__half>(static_cast<const __half*>(x), a);

@@ -92,6 +92,15 @@ int bsi_b200_quantize_pack_clip(const void* x, int dtype, int64_t rows, int64_t 
                                 uint64_t* words, float* scales, int32_t* shifts,
                                 int8_t* q8, int64_t ld8, bsi_stream_t stream);
 
+/* The same again with one more optional output for chunk mode: sq_norms [rows, ceil(D/256)] float32, the sum of
+ * squares of each chunk's de-shifted integers, (2^shift)^2 * sum a^2 (exact; infinity for a chunk that took the
+ * 64-bit fallback). Registered for the int8 image (bsi_b200_register_query_bounds) it lets a dot prove by
+ * Cauchy-Schwarz that its float32 chain cannot round. NULL: bsi_b200_quantize_pack_clip. */
+int bsi_b200_quantize_pack_norms(const void* x, int dtype, int64_t rows, int64_t D, int64_t ldx,
+                                 int decimal_places, int bits, int chunk_mode, float clip_k,
+                                 uint64_t* words, float* scales, int32_t* shifts,
+                                 int8_t* q8, int64_t ld8, float* sq_norms, bsi_stream_t stream);
+
 /* ---- variable-slice mode (the reference's default when no BSI_FIXED_BITS* variable is set) ------
  * The decimal integers v = half_away(double(float(x)) * 10^decimal_places) are sliced as they are,
  * without a shift; the number of slices follows from the largest |v| (bit_width(max|v|) + 2, at least
@@ -189,14 +198,20 @@ int bsi_b200_peer_barrier(uint32_t* const* flags, int rank, int n, int64_t timeo
  * their sum stays below 2^24 in magnitude no float32 addition of the reference's chain rounds, and accumulating the
  * terms as int32 gives the same bits with a third of the epilogue's arithmetic. A prefix is bounded by
  * query_abs_max x (largest 2^shift of the query row) x (sum of |k| over key row r) and by query_abs_max x (sum of the
- * row's 2^shift) x (largest sum of |k| over one 256-element chunk of key row r). With key_abs_sum (device, float32
- * [2, R]: the R row sums, then the R chunk maxima) registered for k8, the tensor-core dots that are handed this k8
- * with this R test the bounds per tile and take the integer route where one holds (the float32 chain elsewhere;
- * results identical either way).
+ * row's 2^shift) x (largest sum of |k| over one 256-element chunk of key row r), and, by Cauchy-Schwarz, by the
+ * product of the L2 norms of the de-shifted query row and of the key row. With key_abs_sum (device, float32 [3, R]:
+ * the R row sums of |k|, the R chunk maxima, the R row sums of k^2) registered for k8, the tensor-core dots that are
+ * handed this k8 with this R test the bounds per tile and take the integer route where one holds (the float32 chain
+ * elsewhere; results identical either way). The third bound also needs the query side
+ * (bsi_b200_register_query_bounds).
  * query_abs_max: largest magnitude of a query integer (64 for 7-bit fixed queries, 128 when unknown). Registering
  * again replaces the entry; unregister before the arrays are freed. BSI_B200_EXACT_INT=0 switches the route off. */
 int bsi_b200_register_key_bounds(const int8_t* k8, const float* key_abs_sum, int64_t R, int query_abs_max);
 int bsi_b200_unregister_key_bounds(const int8_t* k8);
+/* Query side of the Cauchy-Schwarz bound: sq_norms as written by bsi_b200_quantize_pack_norms for the int8 image a8
+ * (stride floats per row, one value per chunk). Dots handed this a8 read it until it is unregistered. */
+int bsi_b200_register_query_bounds(const int8_t* a8, const float* sq_norms, int64_t stride);
+int bsi_b200_unregister_query_bounds(const int8_t* a8);
 /* Test hook: number of (warp, tile) pairs of the paired tensor-core kernel that took the integer route since the
  * last call on this device; synchronises and clears the counter. */
 int bsi_b200_debug_exact_int_tiles(unsigned long long* count_out);

@@ -273,9 +273,10 @@ def test_linear_requant_reports_values_it_cannot_express():
 
 
 def _key_bounds(k8):
-    """[2, R] float32: sum of |k| over each key row, then the largest such sum over one 256-element chunk."""
-    per_chunk = k8.to(torch.int32).abs().view(k8.shape[0], -1, 256).sum(2)
-    return torch.stack([per_chunk.sum(1), per_chunk.amax(1)]).to(torch.float32).contiguous()
+    """[3, R] float32: sum of |k| over each key row, the largest such sum over one 256-element chunk, sum of k^2."""
+    k32 = k8.to(torch.int32)
+    per_chunk = k32.abs().view(k8.shape[0], -1, 256).sum(2)
+    return torch.stack([per_chunk.sum(1), per_chunk.amax(1), (k32 * k32).sum(1)]).to(torch.float32).contiguous()
 
 
 @pytest.mark.parametrize("engine", [3256, 3224, 3128, 3064])
@@ -355,3 +356,47 @@ def test_exact_integer_route_row_scale_and_16bit_outputs():
     _assert_bits(got, want)
     for a, b in zip(y_plain, y_int):
         assert torch.equal(a, b)
+
+
+def test_exact_integer_route_by_the_norm_bound():
+    """FC1-like activations (1 % outliers of 20 sigma) sit at chunk shifts around 7, where the two cheap bounds fail;
+    with the packer's chunk sums of squares registered for the query image the Cauchy-Schwarz bound holds and the
+    integer route runs -- same bits. The sums themselves are checked against the packed integers."""
+    L = capi.lib()
+    Q, R, D = 512, 1024, 2048
+    q, k = _inputs.fc1(Q=Q, R=R, D=D)
+    kb = H.quantize_pack(k.to(DEV), 2, 6, False)
+    chunks = D // 256
+    x = q.to(DEV)
+    words = torch.zeros(Q, 7, D // 64, dtype=torch.int64, device=DEV)
+    scales = torch.ones(Q, chunks, dtype=torch.float32, device=DEV)
+    q8 = torch.zeros(Q, D, dtype=torch.int8, device=DEV)
+    norms = torch.full((Q, chunks), -1.0, dtype=torch.float32, device=DEV)
+    import ctypes as C
+    capi.check(L.bsi_b200_quantize_pack_norms(capi.ptr(x), capi.DTYPE_F16, Q, D, D, 2, 7, 1, C.c_float(0.0), capi.ptr(words),
+                                              capi.ptr(scales), None, capi.ptr(q8), D, capi.ptr(norms), capi.stream_ptr()))
+    want_n = (q8.view(Q, chunks, 256).to(torch.float64) ** 2).sum(2) * scales.to(torch.float64) ** 2
+    assert torch.equal(norms.to(torch.float64), want_n)
+    want, _ = _oracle(q, k)
+    bounds = _key_bounds(kb["q8"])
+    capi.exact_int_tiles()
+    capi.check(L.bsi_b200_register_key_bounds(capi.ptr(kb["q8"]), capi.ptr(bounds), R, 64))
+    try:
+        got_cheap = H.dot_i8(q8, scales, kb["q8"], kb["scales"], o.scale_inv(2), 3256)
+        n_cheap = capi.exact_int_tiles()
+        capi.check(L.bsi_b200_register_query_bounds(capi.ptr(q8), capi.ptr(norms), chunks))
+        got = H.dot_i8(q8, scales, kb["q8"], kb["scales"], o.scale_inv(2), 3256)
+        n_norm = capi.exact_int_tiles()
+    finally:
+        capi.check(L.bsi_b200_unregister_key_bounds(capi.ptr(kb["q8"])))
+        capi.check(L.bsi_b200_unregister_query_bounds(capi.ptr(q8)))
+    _assert_bits(got_cheap, want)
+    _assert_bits(got, want)
+    tiles = 2 * 4 * 16                           # 2 x 4 tiles of 256 x 256, 16 epilogue warps per tile pair
+    assert n_cheap < tiles and n_norm == tiles   # the norm bound covers every warp of every tile
+    # a chunk that took the 64-bit fallback reports infinity, which fails the test safely
+    x2 = x.clone()
+    x2[3, 5] = float("inf")
+    capi.check(L.bsi_b200_quantize_pack_norms(capi.ptr(x2), capi.DTYPE_F16, Q, D, D, 2, 7, 1, C.c_float(0.0), capi.ptr(words),
+                                              capi.ptr(scales), None, capi.ptr(q8), D, capi.ptr(norms), capi.stream_ptr()))
+    assert torch.isinf(norms[3, 0]) and torch.isfinite(norms[3, 1:]).all() and torch.isfinite(norms[4]).all()
