@@ -179,3 +179,25 @@ def test_linear_from_packed_relu_and_column_block_pack():
     yr = bsi_ops.linear_from_packed(q8, sc, cap, bias, 2, torch.float16, True)
     assert torch.equal(yr, torch.relu(want))
     assert (want < 0).any()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_exact_integer_route_does_not_change_the_model(dtype, monkeypatch):
+    """The dots accumulate in integers where a bound proves that exact; with the route switched off the per-linear
+    and the tensor-parallel model give the same logits bit for bit, and the route is actually taken when it is on."""
+    from bsipytorch_b200 import capi
+    from bsipytorch_b200.opt_tp import build_opt_tp
+    cfg = opt.OPTConfig(vocab_size=512, hidden_size=512, num_hidden_layers=2, num_attention_heads=8, ffn_dim=2048,
+                        max_position_embeddings=128, name="tiny512")
+    ids = torch.randint(0, 512, (8, 64), generator=torch.Generator().manual_seed(3)).to(DEV)      # 512 tokens: paired kernel
+    per_linear = opt.build_opt_bsi(cfg, dtype=dtype, device=DEV, seed=7)
+    tp = build_opt_tp(cfg, dtype=dtype, device=DEV, seed=7)
+    capi.exact_int_tiles()
+    with torch.no_grad():
+        on = per_linear(ids), tp(ids)
+    assert capi.exact_int_tiles() > 0
+    monkeypatch.setenv("BSI_B200_EXACT_INT", "0")
+    with torch.no_grad():
+        off = per_linear(ids), tp(ids)
+    assert capi.exact_int_tiles() == 0
+    assert torch.equal(on[0], off[0]) and torch.equal(on[1], off[1])
