@@ -12,7 +12,6 @@
 //   literal w goes to (segments started at or before w) + (literals before w)
 //   RLW = run_bit | (run_len & 0xFFFFFFFF) << 1 | literal_count << 33, written when the segment
 //   closes (at the next start, or at W).
-#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -515,116 +514,6 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_emit_blocks_kernel(
     if (lane == 0) out_len[s] = static_cast<int32_t>(n);
 }
 
-// One-pass encoder: a block takes the next 8 slices in START order (a ticket), holds them in registers, computes
-// their encoded sizes, learns the stream offset of its first slice by a decoupled look-back over the blocks before it
-// (status word per block: state in the top two bits -- 1 = the block's own sum, 2 = the sum of everything up to and
-// including the block -- value below), and emits from the registers. The words are read once. Every wait on a
-// predecessor's status is bounded; a block that gives up sets the device status and stores nothing.
-constexpr u64 kStateShift = 62;
-constexpr u64 kValueMask = (1ull << kStateShift) - 1ull;
-constexpr long long kLookbackLimit = 400000000ll;   // clock64 ticks (~0.2 s); real waits are microseconds
-
-__device__ int g_ewah_status = 0;
-
-template <int TILES>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32) ewah_onepass_kernel(
-    const u64* __restrict__ words, int64_t S, int64_t W, double threshold, const FlagCuts cuts,
-    int32_t* __restrict__ flags, u64 capacity, u64* __restrict__ off, u64* __restrict__ out,
-    int32_t* __restrict__ out_len, u64* __restrict__ status, unsigned int* __restrict__ ticket,
-    u64* __restrict__ total, int64_t nb) {
-    static_assert(TILES > 0, "register-resident slices only");
-    __shared__ u64 wsize[kWarpsPerBlock];
-    __shared__ u64 s_prefix;
-    __shared__ unsigned int s_block;
-    __shared__ int s_ok;
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) s_block = atomicAdd(ticket, 1u);
-    __syncthreads();
-    const int64_t b = s_block;
-    const int64_t s = b * kWarpsPerBlock + warp;
-    u64 wv[TILES];
-    u64 n = 0;
-    int flag = 0;
-    if (s < S) {
-        load_slice<TILES>(words + s * W, W, lane, wv);
-        u64 local = 0;
-#pragma unroll
-        for (int t = 0; t < TILES; ++t) local += static_cast<u64>(__popcll(wv[t]));
-        flag = flag_from(warp_sum_u64(local), W, threshold, cuts);
-        n = encode_slice_regs<false, TILES>(wv, W, flag, nullptr, lane);
-        if (lane == 0) flags[s] = flag;
-    }
-    if (lane == 0) wsize[warp] = n;
-    __syncthreads();
-    if (warp == 0) {
-        u64 mine = lane < kWarpsPerBlock ? wsize[lane] : 0ull;
-        const u64 block_sum = warp_sum_u64(mine);
-        u64 prefix = 0;      // sum of all blocks before this one
-        int ok = 1;
-        volatile u64* st = status;
-        if (b == 0) {
-            if (lane == 0) {
-                __threadfence();
-                st[0] = (2ull << kStateShift) | block_sum;
-            }
-        } else {
-            if (lane == 0) {
-                __threadfence();
-                st[b] = (1ull << kStateShift) | block_sum;
-            }
-            // look back 32 blocks at a time: lane L inspects block j - L
-            int64_t j = b - 1;
-            const long long t0 = clock64();
-            while (true) {
-                const int64_t idx = j - lane;
-                u64 v = 0;
-                if (idx >= 0) {
-                    v = st[idx];
-                    while ((v >> kStateShift) == 0ull) {
-                        if (clock64() - t0 > kLookbackLimit) { ok = 0; break; }
-                        v = st[idx];
-                    }
-                } else {
-                    v = 2ull << kStateShift;          // before block 0: a complete prefix of zero
-                }
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                // the nearest lane holding a complete prefix ends the walk; add the sums of the lanes before it
-                const unsigned full = __ballot_sync(0xffffffffu, (v >> kStateShift) == 2ull);
-                const int stop = full ? __ffs(static_cast<int>(full)) - 1 : 32;
-                const u64 part = warp_sum_u64(lane <= stop ? (v & kValueMask) : 0ull);
-                prefix += part;
-                if (full) break;
-                j -= 32;
-            }
-            if (lane == 0 && ok) {
-                __threadfence();
-                st[b] = (2ull << kStateShift) | ((prefix + block_sum) & kValueMask);
-            }
-        }
-        if (lane == 0) {
-            s_prefix = prefix;
-            s_ok = ok;
-            if (!ok) atomicCAS(&g_ewah_status, 0, 80);
-            if (ok && b == nb - 1 && total != nullptr) *total = prefix + block_sum;
-        }
-    }
-    __syncthreads();
-    if (!s_ok || s >= S) return;
-    u64 before = 0;
-#pragma unroll
-    for (int w = 0; w < kWarpsPerBlock; ++w) before += (w < warp) ? wsize[w] : 0ull;
-    const u64 o = s_prefix + before;
-    if (lane == 0) off[s] = o;
-    if (o + n > capacity) {
-        if (lane == 0) out_len[s] = static_cast<int32_t>(n);
-        return;
-    }
-    const u64 m = encode_slice_regs<true, TILES>(wv, W, flag, out + o, lane);
-    if (lane == 0) out_len[s] = static_cast<int32_t>(m);
-}
-
 // Launch as a programmatic dependent of the kernel before it in the stream: the kernel may start while that one
 // drains and must execute griddepcontrol.wait before it reads what earlier kernels of the stream wrote.
 template <typename... KArgs, typename... Args>
@@ -794,23 +683,6 @@ extern "C" int bsi_b200_ewah_encode(const uint64_t* words, int64_t S, int64_t W,
     if (int rc = flag_cuts(W, threshold, cut_words, stream, &cuts)) return rc;
     const u64* w64 = reinterpret_cast<const u64*>(words);
     const unsigned grid = warp_blocks(S);
-    {
-        const char* e = getenv("BSI_EWAH_ONEPASS");
-        if (e != nullptr && e[0] == '1' && W <= 256 && nb + 2 <= 2 * S + 16 - 3) {
-            u64* status = static_cast<u64*>(scratch);                   // [nb] status words, then the ticket
-            unsigned int* ticket = reinterpret_cast<unsigned int*>(status + nb);
-            BSI_CUDA_TRY(cudaMemsetAsync(status, 0, static_cast<size_t>(nb + 1) * sizeof(u64), stream));
-#define BSI_EWAH_ONE(T) ewah_onepass_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(                              \
-        w64, S, W, threshold, cuts, flags, static_cast<u64>(capacity), reinterpret_cast<u64*>(off),                    \
-        reinterpret_cast<u64*>(out), out_len, status, ticket, reinterpret_cast<u64*>(total), nb)
-            if (W <= 32) BSI_EWAH_ONE(1);
-            else if (W <= 64) BSI_EWAH_ONE(2);
-            else if (W <= 128) BSI_EWAH_ONE(4);
-            else BSI_EWAH_ONE(8);
-#undef BSI_EWAH_ONE
-            return check_launch("ewah_encode one-pass launch");
-        }
-    }
 #define BSI_EWAH_SIZES(T) ewah_sizes_kernel<T><<<grid, kWarpsPerBlock * 32, 0, stream>>>(w64, S, W, threshold, cuts, flags, sizes, block_sums)
     if (W <= 32) BSI_EWAH_SIZES(1);
     else if (W <= 64) BSI_EWAH_SIZES(2);
