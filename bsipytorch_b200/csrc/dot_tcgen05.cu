@@ -557,22 +557,6 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
     if (Q > 0x7fffff00ll || R > 0x7fffff00ll || chunks > 0x400000)
         return fail(BSI_ERR_UNSUPPORTED, "dot_i8: Q, R or chunks too large");
     const bool any_width = y_dtype == BSI_DTYPE_F32;
-    const int bn = force_bn ? force_bn : pick_bn_pair(Q, R, any_width);
-    if (bn < 64 || bn > 256 || (bn & 31) != 0 || (!any_width && (bn & (bn - 1)) != 0))
-        return fail(BSI_ERR_INVALID, "dot_i8: tile width must be a multiple of 32 in [64, 256] (64, 128 or 256 for 16-bit outputs)");
-    if (dbg_iacc != nullptr && y_dtype != BSI_DTYPE_F32)
-        return fail(BSI_ERR_INVALID, "dot_i8: the accumulator dump is only available with float32 output");
-    CUtensorMap ma, mb;
-    if (int rc = make_map(&ma, a8, Q, chunks * 256, lda, BM)) return rc;
-    if (int rc = make_map(&mb, k8, R, chunks * 256, ldk, bn / 2)) return rc;
-    // 16-byte stores need an aligned base, a row pitch that is a multiple of 16 bytes and R a multiple
-    // of the values per 16 bytes; anything else takes the scalar store path
-    const int esz = y_dtype == BSI_DTYPE_F32 ? 4 : 2;
-    const int per16 = 16 / esz;
-    const int vector_store =
-        (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo % per16) == 0 && (R % per16) == 0) ? 1 : 0) |
-        (relu ? 2 : 0);   // the kernel's store_flags
-    const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
     // bounds registered for this key image switch on the integer accumulation where it is provably exact
     KeyBounds kb = {};
     const float* kabs = nullptr;
@@ -588,6 +572,30 @@ int dot_i8_pair(const int8_t* a8, int64_t lda, const float* qs, int64_t qs_strid
             qsq_stride = qb.stride;
         }
     }
+    int bn = force_bn ? force_bn : pick_bn_pair(Q, R, any_width);
+    if (!force_bn && any_width && bn == 256 && kabs != nullptr && qsq != nullptr) {
+        // Both sides carry their bounds, so the integer route is likely, and with its cheaper epilogue a single
+        // wave of 256 x 224 tiles on more pairs beats one of 256 x 256 tiles (measured on 512 x 8192 x 2048:
+        // 13.64 against 13.82 us; with the float32 chain the two are even).
+        const int64_t pairs = sm_count() / 2, mt = (Q + 255) / 256;
+        const int64_t t256 = mt * ((R + 255) / 256), t224 = mt * ((R + 223) / 224);
+        if (t256 <= pairs && t224 <= pairs && t224 > t256) bn = 224;
+    }
+    if (bn < 64 || bn > 256 || (bn & 31) != 0 || (!any_width && (bn & (bn - 1)) != 0))
+        return fail(BSI_ERR_INVALID, "dot_i8: tile width must be a multiple of 32 in [64, 256] (64, 128 or 256 for 16-bit outputs)");
+    if (dbg_iacc != nullptr && y_dtype != BSI_DTYPE_F32)
+        return fail(BSI_ERR_INVALID, "dot_i8: the accumulator dump is only available with float32 output");
+    CUtensorMap ma, mb;
+    if (int rc = make_map(&ma, a8, Q, chunks * 256, lda, BM)) return rc;
+    if (int rc = make_map(&mb, k8, R, chunks * 256, ldk, bn / 2)) return rc;
+    // 16-byte stores need an aligned base, a row pitch that is a multiple of 16 bytes and R a multiple
+    // of the values per 16 bytes; anything else takes the scalar store path
+    const int esz = y_dtype == BSI_DTYPE_F32 ? 4 : 2;
+    const int per16 = 16 / esz;
+    const int vector_store =
+        (((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ldo % per16) == 0 && (R % per16) == 0) ? 1 : 0) |
+        (relu ? 2 : 0);   // the kernel's store_flags
+    const int q = static_cast<int>(Q), r = static_cast<int>(R), c = static_cast<int>(chunks);
 #define BSI_PAIR_T(BN_, DBG_, T_)                                                                              \
     launch_pair<BN_, DBG_, T_>(ma, mb, vector_store, qs, qs_stride, bw0, bias, q, r, c, scale_inv, out, ldo,  \
                                dbg_iacc, scatter, requant, kabs, qabs, qsq, qsq_stride, stream)
