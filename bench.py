@@ -41,7 +41,7 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one dot launch, from the ncu capture summarised
 # under profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"fc1": 17945856, "fc2": 21090000, "pack": 134321152 + 85714944, "pack-lean": 134263552 + 39758592,
+NCU_TRAFFIC_BYTES = {"fc1": 18061056, "fc2": 21090000, "pack": 134321152 + 85714944, "pack-lean": 134263552 + 39758592,
                      "ewah": 58746112 + 39424 + 59124992 + 8368384}
 
 
